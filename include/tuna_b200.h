@@ -1,0 +1,125 @@
+/*
+ * tuna_b200 — C ABI of the B200 (sm_100a) FP16 x 4-bit(codebook) GEMM.
+ *
+ * Drop-in boundary for the two host launchers behind TryForefront/tuna's torch
+ * extension (extension.cpp:22-24).  Plain pointers and sizes only; every
+ * pointer is DEVICE memory owned by the caller unless stated otherwise; every
+ * call is enqueued on `stream` (a cudaStream_t passed as void*) and returns
+ * without synchronising.  All entry points return TUNA_OK (0) or a negative
+ * tuna_status; nothing is launched when the status is negative.
+ *
+ * Names follow the reference: m = output features (rows of W), n = tokens,
+ * k = reduction length.  Layouts (reference file:line):
+ *   x       fp16  [n, k]          row-major activations        (test.py:76)
+ *   q       u8    [m/8, k/8, 32]  packed 4-bit codes; byte j of tile (mt,kt)
+ *                                 holds W[8mt+j/4, 8kt+2(j%4)] in its HIGH and
+ *                                 W[.., 8kt+2(j%4)+1] in its LOW nibble
+ *                                 (test.py:55-65, kernel.cu:3171,3221-3228)
+ *   absmax  fp32  [m]             one scale per output row     (test.py:16-18)
+ *   code    fp32  [16]            codebook, passed per call    (test.py:19-40)
+ *   o       fp16  [n, m]          row-major output             (test.py:79)
+ */
+#ifndef TUNA_B200_H
+#define TUNA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum tuna_status {
+    TUNA_OK = 0,
+    TUNA_ERR_NULL_POINTER = -1,    /* a required pointer is NULL                        */
+    TUNA_ERR_BAD_SHAPE = -2,       /* m, k not positive multiples of 8, or n < 1        */
+    TUNA_ERR_MISALIGNED = -3,      /* a pointer misses its required alignment           */
+    TUNA_ERR_WORKSPACE = -4,       /* workspace NULL/too small for this shape           */
+    TUNA_ERR_BAD_CONFIG = -5,      /* explicit launch config is inconsistent            */
+    TUNA_ERR_LAUNCH = -6,          /* the CUDA runtime refused the launch               */
+    TUNA_ERR_NO_DEVICE = -7,       /* no sm_100 device / kernel image not loadable      */
+    TUNA_ERR_DEVICE_TIMEOUT = -8,  /* a bounded in-kernel wait ran out (status word)    */
+    TUNA_ERR_TOO_LARGE = -9        /* beyond a documented size limit                    */
+} tuna_status;
+
+/* Which kernel family a launch uses.  AUTO lets the shape table decide. */
+typedef enum tuna_path {
+    TUNA_PATH_AUTO = 0,
+    TUNA_PATH_STREAM = 1, /* mma.sync weight-streaming kernel, tokens <= 16 per pass  */
+    TUNA_PATH_UMMA = 2    /* tcgen05/TMEM kernel: TMA-staged, dequant into TMEM       */
+} tuna_path;
+
+/* Launch configuration, the Blackwell counterpart of the reference's
+ * KernelConfig (configs.cu:12-54).  Produced by the shape table generated from
+ * param_map.json, or filled by hand (tuner, tests).  Zero means "default". */
+typedef struct tuna_config {
+    int32_t path;          /* tuna_path                                               */
+    int32_t tile_tok;      /* tokens per pass: stream 8|16; umma 16..256 (mult of 16) */
+    int32_t rows_per_warp; /* stream: 32-row blocks per warp (1|2|4)                  */
+    int32_t warps_m;       /* stream: warps along output rows                         */
+    int32_t warps_k;       /* stream: warps along K inside a CTA                      */
+    int32_t split_k;       /* stream: CTAs along K (workspace reduce when > 1)        */
+    int32_t ctas;          /* umma: persistent CTAs (0 = one per SM)                  */
+    int32_t stages_w;      /* umma: packed-weight ring depth (64-k stages)            */
+    int32_t stages_x;      /* umma: activation ring depth                             */
+    int32_t dequant_warps; /* umma: warps converting codes into TMEM (mult of 4)      */
+    int32_t reserved[6];
+} tuna_config;
+
+/*
+ * o[n, m] = x[n, k] * dequant(q)[m, k]^T, fp16 operands, fp32 accumulation,
+ * one fp16 rounding.  Replaces `wrapper` (kernel.cu:3009-3156) and keeps its
+ * argument order (q, x, code, absmax, o — extension.cpp:29-33 reorders the
+ * Python arguments into it).  Differences, all supersets of the reference:
+ * `o` is overwritten (no pre-zeroing needed, a pre-zeroed `o` is also fine);
+ * every (m % 8 == 0, k % 8 == 0, n >= 1) shape runs instead of only the 14
+ * tabulated ones; results are bit-identical from run to run.
+ * `workspace` holds split-K partial sums and tile counters; its first
+ * tuna_matmul_workspace_bytes() bytes must be ZERO before the first call and
+ * are left zeroed-where-needed by every call, so one allocation can be reused
+ * by consecutive calls on the same stream (calls that overlap on the device
+ * need separate workspaces).  Alignment: q, x, o, workspace 16 bytes; absmax,
+ * code 4 bytes.
+ */
+int tuna_matmul(const void *q, const void *x, const void *code, const void *absmax, void *o,
+                int m, int n, int k, void *workspace, size_t workspace_bytes, void *stream);
+
+/* As tuna_matmul, with an explicit launch configuration (tuner, tests). */
+int tuna_matmul_cfg(const void *q, const void *x, const void *code, const void *absmax, void *o,
+                    int m, int n, int k, void *workspace, size_t workspace_bytes, void *stream,
+                    const tuna_config *cfg);
+
+/* Upper bound, over every configuration the table can pick for this shape, of
+ * the workspace tuna_matmul needs.  Host-only arithmetic, no CUDA call. */
+size_t tuna_matmul_workspace_bytes(int m, int n, int k);
+
+/* The configuration tuna_matmul would use for (m, n, k) on the current device:
+ * exact table entry if param_map.json had one for the shape and token bucket,
+ * otherwise a heuristic.  Replaces the 122-arm if-chain of kernel.cu:3022-3155;
+ * unlike it, an unknown shape is never a silent no-op. */
+int tuna_lookup_config(int m, int n, int k, tuna_config *out);
+
+/*
+ * o[m, k] (fp16) = fp16_rn(fp32(code[nibble]) * fp32(absmax[row])).  Replaces
+ * `dequantize_wrapper` (kernel.cu:3243-3253) and is bit-exact to its kernel
+ * (kernel.cu:3218-3229).  Works for any m % 8 == 0, k % 8 == 0 (the reference
+ * needs multiples of 64).
+ */
+int tuna_dequant(const void *q, const void *absmax, const void *code, void *o,
+                 int m, int k, void *stream);
+
+/* Reads and clears the device status word of the last tcgen05 launch on the
+ * current device (synchronises `stream`).  TUNA_OK, or
+ * TUNA_ERR_DEVICE_TIMEOUT if a bounded mbarrier wait gave up. */
+int tuna_check_device_status(void *stream);
+
+const char *tuna_status_string(int status);
+
+/* Library / table identification: ABI version and number of table entries. */
+int tuna_abi_version(void);
+int tuna_config_table_size(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TUNA_B200_H */

@@ -1,0 +1,77 @@
+"""ctypes binding of libtuna_b200.so (the C ABI in include/tuna_b200.h)."""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int32, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libtuna_b200.so"
+
+
+class TunaConfig(ctypes.Structure):
+    """Mirror of `struct tuna_config`."""
+
+    _fields_ = [
+        ("path", c_int32),
+        ("tile_tok", c_int32),
+        ("rows_per_warp", c_int32),
+        ("warps_m", c_int32),
+        ("warps_k", c_int32),
+        ("split_k", c_int32),
+        ("ctas", c_int32),
+        ("stages_w", c_int32),
+        ("stages_x", c_int32),
+        ("dequant_warps", c_int32),
+        ("reserved", c_int32 * 6),
+    ]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}
+
+
+PATH_AUTO, PATH_STREAM, PATH_UMMA = 0, 1, 2
+
+# every symbol include/tuna_b200.h declares: name -> (restype, argtypes)
+SYMBOLS = {
+    "tuna_matmul": (c_int, [c_void_p] * 5 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),
+    "tuna_matmul_cfg": (c_int, [c_void_p] * 5 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p, ctypes.POINTER(TunaConfig)]),
+    "tuna_matmul_workspace_bytes": (c_size_t, [c_int] * 3),
+    "tuna_lookup_config": (c_int, [c_int] * 3 + [ctypes.POINTER(TunaConfig)]),
+    "tuna_dequant": (c_int, [c_void_p] * 4 + [c_int] * 2 + [c_void_p]),
+    "tuna_check_device_status": (c_int, [c_void_p]),
+    "tuna_status_string": (c_char_p, [c_int]),
+    "tuna_abi_version": (c_int, []),
+    "tuna_config_table_size": (c_int, []),
+}
+
+_lib = None
+
+
+def load():
+    """Load the shared library, failing loudly when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m tuna_b200.build` "
+                "(there is no fallback implementation)"
+            )
+        lib = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+class TunaError(RuntimeError):
+    def __init__(self, status: int):
+        self.status = status
+        super().__init__(f"tuna_b200: {load().tuna_status_string(status).decode()} (status {status})")
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise TunaError(status)

@@ -1,0 +1,37 @@
+// Internal launcher interface between the C ABI (tuna_api.cu) and the kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+#include "../../include/tuna_b200.h"
+
+namespace tuna {
+
+struct GemmArgs {
+    const uint8_t *q;
+    const void *x;       // fp16 [n, k]
+    const float *code;   // [16]
+    const float *absmax; // [m]
+    void *o;             // fp16 [n, m]
+    int m, n, k;
+    void *workspace;
+    size_t workspace_bytes;
+    cudaStream_t stream;
+    int sm_count;
+};
+
+cudaError_t launch_dequant(const void *q, const void *absmax, const void *code, void *o, int m,
+                           int k, int sm_count, cudaStream_t stream);
+
+// mma.sync weight-streaming kernel.  Returns a tuna_status.
+int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg);
+size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &cfg);
+int gemm_stream_normalize_config(int m, int n, int k, int sm_count, tuna_config *cfg);
+
+// tcgen05/TMEM kernel.  Returns a tuna_status.
+int launch_gemm_umma(const GemmArgs &a, const tuna_config &cfg);
+size_t gemm_umma_workspace_bytes(int m, int n, int k, const tuna_config &cfg, int sm_count);
+int gemm_umma_normalize_config(int m, int n, int k, int sm_count, tuna_config *cfg);
+int gemm_umma_read_status(cudaStream_t stream);
+
+}  // namespace tuna

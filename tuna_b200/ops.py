@@ -1,0 +1,110 @@
+"""Host-side mirror of the reference's two ops (extension.cpp:26-49).
+
+The reference performs no checks at all (no dtype, device, contiguity or shape
+validation, extension.cpp:26-49; unknown shapes silently do nothing,
+kernel.cu:3022-3155).  The mirror keeps the call signature and adds the checks:
+a bad argument raises instead of corrupting memory.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import TunaConfig, check
+
+_workspaces: dict = {}
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _expect(t: torch.Tensor, name: str, dtype, numel: int, device=None):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if device is not None and t.device != device:
+        raise ValueError(f"{name} is on {t.device}, expected {device}")
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if t.numel() != numel:
+        raise ValueError(f"{name} has {t.numel()} elements, expected {numel}")
+
+
+def workspace_for(m: int, n: int, k: int, device) -> torch.Tensor:
+    """A zero-initialised per-(device, stream) workspace large enough for (m, n, k).
+
+    The kernels leave the workspace clean after every call, so one buffer serves
+    consecutive calls on a stream; it only grows.
+    """
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        need = int(lib.tuna_matmul_workspace_bytes(m, n, k))
+    key = (torch.device(device).index, _stream_ptr(device))
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def lookup_config(m: int, n: int, k: int) -> TunaConfig:
+    cfg = TunaConfig()
+    check(_lib.load().tuna_lookup_config(m, n, k, ctypes.byref(cfg)))
+    return cfg
+
+
+def matmul(x, q, s, c, o, m: int, n: int, k: int, *, config: TunaConfig | None = None, workspace=None) -> None:
+    """`tuna.matmul(x, q, s, c, o, m, n, k)` (extension.cpp:26-38).
+
+    x fp16 [n,k]; q uint8 [m/8,k/8,32]; s fp32 [m] (absmax); c fp32 [16]
+    (codebook); o fp16 [n,m], overwritten.  Enqueued on the current stream of
+    x's device.
+    """
+    dev = x.device if isinstance(x, torch.Tensor) else None
+    _expect(x, "x", torch.float16, n * k)
+    _expect(q, "q", torch.uint8, m * k // 2, dev)
+    _expect(s, "s", torch.float32, m, dev)
+    _expect(c, "c", torch.float32, 16, dev)
+    _expect(o, "o", torch.float16, n * m, dev)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        ws = workspace if workspace is not None else workspace_for(m, n, k, dev)
+        args = (q.data_ptr(), x.data_ptr(), c.data_ptr(), s.data_ptr(), o.data_ptr(), m, n, k,
+                ws.data_ptr(), ws.numel() * ws.element_size(), _stream_ptr(dev))
+        if config is None:
+            check(lib.tuna_matmul(*args))
+        else:
+            check(lib.tuna_matmul_cfg(*args, ctypes.byref(config)))
+
+
+def dequant(q, absmax, codebook, o, m: int, k: int) -> None:
+    """`tuna.dequant(q, absmax, codebook, o, m, k)` (extension.cpp:40-49); o fp16 [m,k]."""
+    dev = q.device if isinstance(q, torch.Tensor) else None
+    _expect(q, "q", torch.uint8, m * k // 2)
+    _expect(absmax, "absmax", torch.float32, m, dev)
+    _expect(codebook, "codebook", torch.float32, 16, dev)
+    _expect(o, "o", torch.float16, m * k, dev)
+    with torch.cuda.device(dev):
+        check(_lib.load().tuna_dequant(q.data_ptr(), absmax.data_ptr(), codebook.data_ptr(), o.data_ptr(),
+                                       m, k, _stream_ptr(dev)))
+
+
+def matmul_host(x_host, q, s, c, o_host, m: int, n: int, k: int, *, x_dev=None, o_dev=None) -> None:
+    """The op with HOST activations and output: copies x (pinned host) to the device, runs the
+    GEMM against the resident weights and copies the result back, all on the current stream.
+    Weights, scales and codebook are parameters and stay on the device, as in the reference."""
+    dev = q.device
+    if x_dev is None:
+        x_dev = torch.empty((n, k), dtype=torch.float16, device=dev)
+    if o_dev is None:
+        o_dev = torch.empty((n, m), dtype=torch.float16, device=dev)
+    x_dev.copy_(x_host, non_blocking=True)
+    matmul(x_dev, q, s, c, o_dev, m, n, k)
+    o_host.copy_(o_dev, non_blocking=True)

@@ -1,0 +1,211 @@
+"""Parity of the CUDA path against the oracle, through the C ABI, on a B200."""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import tuna_oracle as orc
+from tuna_b200 import _lib
+from tests.gpu_util import Guarded, check_parity, make_case, run_matmul, stream_ptr, to_dev
+
+pytestmark = pytest.mark.gpu
+
+# max relative error budget of the GEMM: 1e-2 (fp32 accumulation on both sides)
+TOL = 1e-2
+
+
+# ----------------------------------------------------------------- dequant: bit exact
+
+@pytest.mark.parametrize("m,k", [(8, 8), (64, 64), (72, 136), (128, 4096), (4096, 4096), (1000 * 8, 264)])
+def test_dequant_bit_exact(m, k):
+    lib = _lib.load()
+    (x, q, absmax, code), (xd, qd, sd, cd) = make_case(m, 1, k, seed=m + k)
+    out = Guarded(m * k * 2, torch.float16, (m, k))
+    st = lib.tuna_dequant(qd.data_ptr(), sd.data_ptr(), cd.data_ptr(), out.view.data_ptr(), m, k, stream_ptr())
+    torch.cuda.synchronize()
+    assert st == 0
+    ref = orc.dequant_ref(q, absmax, code, m, k)
+    got = out.view.cpu().numpy()
+    assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
+    assert out.guards_intact()
+
+
+def test_dequant_arbitrary_codebook_and_scales():
+    lib = _lib.load()
+    m, k = 256, 512
+    rng = np.random.default_rng(9)
+    codes = rng.integers(0, 16, (m, k), dtype=np.uint8)
+    q = orc.pack_codes(codes)
+    code = rng.standard_normal(16).astype(np.float32)
+    absmax = np.exp(rng.uniform(-12, 6, m)).astype(np.float32)  # includes fp16 subnormal products and overflow
+    qd, sd, cd = to_dev(q, absmax, code)
+    out = torch.empty((m, k), dtype=torch.float16, device="cuda")
+    assert lib.tuna_dequant(qd.data_ptr(), sd.data_ptr(), cd.data_ptr(), out.data_ptr(), m, k, stream_ptr()) == 0
+    torch.cuda.synchronize()
+    ref = orc.dequant_ref(q, absmax, code, m, k)
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), ref.view(np.uint16))
+
+
+# ----------------------------------------------------------------- GEMM: tolerance 1e-2
+
+SMALL_SHAPES = [  # (m, k): awkward sizes, partial tiles, k not a multiple of 32
+    (8, 8), (64, 64), (128, 64), (136, 72), (520, 264), (1024, 1024), (4104, 520),
+]
+
+
+@pytest.mark.parametrize("n", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("m,k", SMALL_SHAPES)
+def test_matmul_small_shapes(m, k, n):
+    host, dev = make_case(m, n, k, seed=m * 7 + k + n)
+    st, out, holder = run_matmul(dev, m, n, k)
+    assert st == 0, _lib.load().tuna_status_string(st)
+    ref = orc.matmul_ref(*host, m, n, k)
+    check_parity(out.cpu().numpy(), ref, TOL)
+    assert holder.guards_intact()
+
+
+BASELINE_SHAPES = [
+    (6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336),
+    (10240, 8192), (8192, 8192), (57344, 8192), (8192, 28672),
+]
+
+
+@pytest.mark.parametrize("m,k", BASELINE_SHAPES)
+def test_matmul_baseline_shapes_m16(m, k):
+    """Full benchmark sizes; the oracle runs on a random sample of output rows."""
+    n = 16
+    (x, q, absmax, code), dev = make_case(m, n, k, seed=m + k)
+    st, out, holder = run_matmul(dev, m, n, k)
+    assert st == 0
+    rng = np.random.default_rng(0)
+    rows = np.unique(np.concatenate([rng.integers(0, m // 8, 48), [0, m // 8 - 1]]))
+    q3 = q.reshape(m // 8, k // 8, 32)
+    ref = orc.matmul_ref(x, q3[rows], absmax.reshape(-1, 8)[rows].ravel(), code, len(rows) * 8, n, k)
+    got = out.cpu().numpy().reshape(n, m // 8, 8)[:, rows].reshape(n, -1)
+    check_parity(got, ref, TOL)
+    assert holder.guards_intact()
+
+
+def test_matmul_linearity_full_size():
+    """Size-independent property at a full benchmark size: the op is linear in x, so
+    f(x1 + x2) == f(x1) + f(x2) up to fp16 rounding of the three outputs."""
+    m, n, k = 28672, 16, 4096
+    (x, q, absmax, code), (xd, qd, sd, cd) = make_case(m, n, k, seed=5)
+    x2 = np.random.default_rng(6).standard_normal((n, k)).astype(np.float16)
+    x2d, = to_dev(x2)
+    xsum = (xd.float() + x2d.float()).half()
+    outs = []
+    for xin in (xd, x2d, xsum):
+        st, o, _ = run_matmul((xin, qd, sd, cd), m, n, k)
+        assert st == 0
+        outs.append(o.float())
+    # compare against the sum computed from the rounded inputs' exact linear combination
+    lhs = outs[2]
+    rhs = outs[0] + outs[1]
+    err = (lhs - rhs).abs().max().item() / rhs.abs().max().item()
+    assert err < 4e-3, err
+
+
+@pytest.mark.parametrize("m,k,n", [(4096, 4096, 16), (4096, 14336, 16), (520, 264, 5)])
+def test_matmul_is_deterministic_and_needs_no_zero_fill(m, k, n):
+    host, dev = make_case(m, n, k, seed=1)
+    ws = torch.zeros(64 << 20, dtype=torch.uint8, device="cuda")
+    first = None
+    for it in range(10):
+        out = torch.full((n, m), float("nan"), dtype=torch.float16, device="cuda")  # garbage on purpose
+        st, out, _ = run_matmul(dev, m, n, k, out=out, ws=ws)
+        assert st == 0
+        got = out.cpu().numpy().view(np.uint16)
+        if first is None:
+            first = got
+        else:
+            assert np.array_equal(first, got), f"run {it} differs"
+    # the workspace is left clean: only partial sums may remain, counters are zero again
+    cfg = _lib.TunaConfig()
+    _lib.load().tuna_lookup_config(m, n, k, ctypes.byref(cfg))
+    if cfg.path == _lib.PATH_STREAM:
+        tiles = -(-m // (32 * cfg.rows_per_warp * cfg.warps_m))
+        assert int(ws[: tiles * 4].view(torch.int32).abs().sum()) == 0
+
+
+STREAM_CONFIGS = [
+    dict(rows_per_warp=r, warps_m=wm, warps_k=wk, split_k=sk, tile_tok=tt)
+    for (r, wm, wk, sk, tt) in [
+        (1, 1, 1, 1, 16), (1, 16, 1, 1, 16), (1, 1, 16, 1, 16), (2, 4, 4, 1, 16), (4, 4, 4, 1, 16),
+        (4, 2, 8, 3, 16), (2, 8, 2, 7, 16), (1, 4, 4, 2, 8), (4, 16, 1, 4, 8), (2, 2, 2, 5, 8),
+    ]
+]
+
+
+@pytest.mark.parametrize("cfgd", STREAM_CONFIGS)
+@pytest.mark.parametrize("m,k,n", [(1024, 2048, 16), (4104, 520, 7)])
+def test_stream_kernel_every_template_and_split(m, k, n, cfgd):
+    host, dev = make_case(m, n, k, seed=3)
+    cfg = _lib.TunaConfig(path=_lib.PATH_STREAM, **cfgd)
+    st, out, holder = run_matmul(dev, m, n, k, cfg=cfg)
+    assert st == 0, _lib.load().tuna_status_string(st)
+    check_parity(out.cpu().numpy(), orc.matmul_ref(*host, m, n, k), TOL)
+    assert holder.guards_intact()
+
+
+def test_matmul_extreme_values():
+    """Codes all at the ends of the codebook and large activations: no overflow inside the
+    fp32 accumulation, fp16 result saturates only where the oracle's does."""
+    m, n, k = 256, 16, 1024
+    rng = np.random.default_rng(2)
+    codes = rng.choice(np.array([0, 15], dtype=np.uint8), size=(m, k))
+    q = orc.pack_codes(codes)
+    absmax = np.full(m, 0.02, dtype=np.float32)
+    x = (rng.standard_normal((n, k)) * 30).astype(np.float16)
+    code = orc.NF4_CODE.copy()
+    dev = to_dev(x, q, absmax, code)
+    st, out, _ = run_matmul(dev, m, n, k)
+    assert st == 0
+    check_parity(out.cpu().numpy(), orc.matmul_ref(x, q, absmax, code, m, n, k), TOL)
+
+
+def test_golden_fixtures_against_cuda():
+    """The committed reference-kernel outputs, compared with the CUDA path directly."""
+    from pathlib import Path
+
+    files = sorted((Path(__file__).parent / "golden").glob("ref_*.npz"))
+    if not files:
+        pytest.skip("no reference fixtures committed yet")
+    lib = _lib.load()
+    for path in files:
+        z = np.load(path)
+        m, n, k, seed = (int(z[s]) for s in ("m", "n", "k", "seed"))
+        (x, q, absmax, code), dev = make_case(m, n, k, seed)
+        if "matmul" in z:
+            st, out, _ = run_matmul(dev, m, n, k)
+            assert st == 0
+            check_parity(out.cpu().numpy(), z["matmul"].view(np.float16), 2e-2)
+        if "dequant_sample" in z:
+            o = torch.empty((m, k), dtype=torch.float16, device="cuda")
+            assert lib.tuna_dequant(dev[1].data_ptr(), dev[2].data_ptr(), dev[3].data_ptr(), o.data_ptr(), m, k, stream_ptr()) == 0
+            torch.cuda.synchronize()
+            got = o.cpu().numpy()[z["dequant_rows"]]
+            assert np.array_equal(got.view(np.uint16), z["dequant_sample"])
+
+
+def test_python_mirror_matches_c_abi():
+    import tuna_b200
+
+    m, n, k = 1024, 16, 1024
+    host, (xd, qd, sd, cd) = make_case(m, n, k, seed=8)
+    o = torch.empty((n, m), dtype=torch.float16, device="cuda")
+    tuna_b200.matmul(xd, qd, sd, cd, o, m, n, k)
+    torch.cuda.synchronize()
+    check_parity(o.cpu().numpy(), orc.matmul_ref(*host, m, n, k), TOL)
+    w = torch.empty((m, k), dtype=torch.float16, device="cuda")
+    tuna_b200.dequant(qd, sd, cd, w, m, k)
+    torch.cuda.synchronize()
+    assert np.array_equal(w.cpu().numpy().view(np.uint16), orc.dequant_ref(host[1], host[2], host[3], m, k).view(np.uint16))
+    with pytest.raises(TypeError):
+        tuna_b200.matmul(xd.float(), qd, sd, cd, o, m, n, k)
+    with pytest.raises(ValueError):
+        tuna_b200.matmul(xd, qd, sd, cd, o, m, n + 1, k)
+    with pytest.raises(ValueError):
+        tuna_b200.matmul(xd.cpu(), qd, sd, cd, o, m, n, k)

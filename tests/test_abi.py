@@ -57,25 +57,31 @@ def test_argument_validation_needs_no_gpu(tuna_lib):
     assert tuna_lib.tuna_matmul_workspace_bytes(60, 1, 64) == 0
 
 
-def test_workspace_required_when_split_k(tuna_lib):
-    # a K-heavy, row-poor shape gets split-K from the heuristic and must then be given a workspace
-    cfg = _lib.TunaConfig()
-    assert tuna_lib.tuna_lookup_config(4096, 16, 14336, ctypes.byref(cfg)) == 0
+def test_workspace_is_always_required(tuna_lib):
+    # both kernels are persistent and finish tiles cut across CTAs through the workspace
     need = tuna_lib.tuna_matmul_workspace_bytes(4096, 16, 14336)
-    if cfg.path == _lib.PATH_STREAM and cfg.split_k > 1:
-        assert need > 0
-        buf = ctypes.create_string_buffer(256)
-        p = ctypes.c_void_p((ctypes.addressof(buf) + 63) & ~63)
-        assert tuna_lib.tuna_matmul(p, p, p, p, p, 4096, 16, 14336, None, 0, None) == -4
-        assert tuna_lib.tuna_matmul(p, p, p, p, p, 4096, 16, 14336, p, 16, None) == -4
+    assert need > 0
+    buf = ctypes.create_string_buffer(256)
+    p = ctypes.c_void_p((ctypes.addressof(buf) + 63) & ~63)
+    assert tuna_lib.tuna_matmul(p, p, p, p, p, 4096, 16, 14336, None, 0, None) == -4
+    assert tuna_lib.tuna_matmul(p, p, p, p, p, 4096, 16, 14336, p, 16, None) == -4
 
 
 def test_bad_explicit_config_is_rejected(tuna_lib):
     buf = ctypes.create_string_buffer(256)
     p = ctypes.c_void_p((ctypes.addressof(buf) + 63) & ~63)
-    cfg = _lib.TunaConfig(path=_lib.PATH_STREAM, tile_tok=16, rows_per_warp=3, warps_m=4, warps_k=4, split_k=1)
-    assert tuna_lib.tuna_matmul_cfg(p, p, p, p, p, 512, 16, 512, p, 64, None, ctypes.byref(cfg)) == -5
-    cfg = _lib.TunaConfig(path=_lib.PATH_STREAM, tile_tok=16, rows_per_warp=2, warps_m=8, warps_k=4, split_k=1)
-    assert tuna_lib.tuna_matmul_cfg(p, p, p, p, p, 512, 16, 512, p, 64, None, ctypes.byref(cfg)) == -5  # 32 warps
-    cfg = _lib.TunaConfig(path=7)
-    assert tuna_lib.tuna_matmul_cfg(p, p, p, p, p, 512, 16, 512, p, 64, None, ctypes.byref(cfg)) == -5
+    big = 1 << 30
+
+    def call(**kw):
+        cfg = _lib.TunaConfig(**kw)
+        return tuna_lib.tuna_matmul_cfg(p, p, p, p, p, 512, 16, 512, p, big, None, ctypes.byref(cfg))
+
+    assert call(path=_lib.PATH_STREAM, tile_tok=16, rows_per_warp=3, warps_m=4, warps_k=4) == -5
+    assert call(path=_lib.PATH_STREAM, tile_tok=16, rows_per_warp=2, warps_m=8, warps_k=4) == -5   # 32 warps
+    assert call(path=_lib.PATH_STREAM, tile_tok=16, rows_per_warp=1, warps_m=3, warps_k=4) == -5   # not a power of 2
+    assert call(path=_lib.PATH_STREAM, tile_tok=24) == -5
+    assert call(path=_lib.PATH_STREAM, tile_tok=32, rows_per_warp=2) == -5                         # accumulators
+    assert call(path=_lib.PATH_UMMA, tile_tok=48) == -5
+    assert call(path=_lib.PATH_UMMA, tile_tok=256, row_blocks=2) == -5                             # TMEM columns
+    assert call(path=_lib.PATH_UMMA, tile_tok=16, dequant_warps=6) == -5
+    assert call(path=7) == -5

@@ -128,13 +128,15 @@ def test_matmul_is_deterministic_and_needs_no_zero_fill(m, k, n):
     if cfg.path == _lib.PATH_STREAM:
         tiles = -(-m // (32 * cfg.rows_per_warp * cfg.warps_m))
         assert int(ws[: tiles * 4].view(torch.int32).abs().sum()) == 0
+    assert _lib.load().tuna_check_device_status(stream_ptr()) == 0
 
 
 STREAM_CONFIGS = [
-    dict(rows_per_warp=r, warps_m=wm, warps_k=wk, split_k=sk, tile_tok=tt)
-    for (r, wm, wk, sk, tt) in [
-        (1, 1, 1, 1, 16), (1, 16, 1, 1, 16), (1, 1, 16, 1, 16), (2, 4, 4, 1, 16), (4, 4, 4, 1, 16),
-        (4, 2, 8, 3, 16), (2, 8, 2, 7, 16), (1, 4, 4, 2, 8), (4, 16, 1, 4, 8), (2, 2, 2, 5, 8),
+    dict(rows_per_warp=r, warps_m=wm, warps_k=wk, k_steps=ks, tile_tok=tt, ctas=ctas)
+    for (r, wm, wk, ks, tt, ctas) in [
+        (1, 1, 1, 1, 16, 0), (1, 16, 1, 2, 16, 0), (1, 1, 16, 1, 16, 0), (2, 4, 4, 2, 16, 0), (2, 16, 1, 1, 16, 0),
+        (2, 2, 8, 2, 16, 3), (2, 8, 2, 1, 16, 7), (1, 4, 4, 2, 8, 0), (2, 16, 1, 2, 8, 5), (2, 2, 2, 1, 8, 148),
+        (1, 8, 2, 2, 32, 0), (1, 2, 4, 1, 32, 11),
     ]
 ]
 
@@ -146,6 +148,19 @@ def test_stream_kernel_every_template_and_split(m, k, n, cfgd):
     cfg = _lib.TunaConfig(path=_lib.PATH_STREAM, **cfgd)
     st, out, holder = run_matmul(dev, m, n, k, cfg=cfg)
     assert st == 0, _lib.load().tuna_status_string(st)
+    assert _lib.load().tuna_check_device_status(stream_ptr()) == 0, "a bounded wait ran out"
+    check_parity(out.cpu().numpy(), orc.matmul_ref(*host, m, n, k), TOL)
+    assert holder.guards_intact()
+
+
+@pytest.mark.parametrize("n", [17, 31, 32, 40])
+def test_stream_kernel_token_passes(n):
+    """More tokens than one pass holds: the launcher loops over token groups."""
+    m, k = 520, 264
+    host, dev = make_case(m, n, k, seed=n)
+    cfg = _lib.TunaConfig(path=_lib.PATH_STREAM, tile_tok=16)
+    st, out, holder = run_matmul(dev, m, n, k, cfg=cfg)
+    assert st == 0
     check_parity(out.cpu().numpy(), orc.matmul_ref(*host, m, n, k), TOL)
     assert holder.guards_intact()
 

@@ -18,12 +18,15 @@ class TunaConfig(ctypes.Structure):
         ("rows_per_warp", c_int32),
         ("warps_m", c_int32),
         ("warps_k", c_int32),
-        ("split_k", c_int32),
+        ("k_steps", c_int32),
         ("ctas", c_int32),
         ("stages_w", c_int32),
         ("stages_x", c_int32),
         ("dequant_warps", c_int32),
-        ("reserved", c_int32 * 6),
+        ("row_blocks", c_int32),
+        ("stages_a", c_int32),
+        ("k_accs", c_int32),
+        ("reserved", c_int32 * 3),
     ]
 
     def as_dict(self):

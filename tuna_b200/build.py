@@ -16,7 +16,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libtuna_b200.so"
-SOURCES = ["tuna_api.cu", "dequant_sm100a.cu", "gemm_stream_sm100a.cu", "gemm_umma_sm100a.cu"]
+SOURCES = ["tuna_api.cu", "host_util.cu", "dequant_sm100a.cu", "gemm_stream_sm100a.cu", "gemm_umma_sm100a.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
@@ -53,7 +53,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     def compile_one(src: str):
         obj = objdir / (src + ".o")
         if force or _stale(obj, [CSRC / src] + headers):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", str(CSRC / src), "-o", str(obj)]
+            extra = os.environ.get("TUNA_EXTRA_NVCC_FLAGS", "").split()
+            cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", str(CSRC / src), "-o", str(obj)]
             r = subprocess.run(cmd, capture_output=True, text=True)
             if verbose or r.returncode:
                 sys.stderr.write(r.stdout + r.stderr)

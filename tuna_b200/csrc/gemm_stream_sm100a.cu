@@ -1,54 +1,75 @@
-// Weight-streaming FP16 x 4-bit(codebook) GEMM for small token counts (n <= 16
-// per pass), sm_100a.  Counterpart of the reference's Tuna<> kernel and its
-// Deq4GemmIterator main loop (kernel.cu:1043-2505, 2816-2960) for the
-// memory-bound regime; same mma orientation (weights are the m16 "A" operand,
-// tokens the n8 "B" operand, kernel.cu:2182-2192), nothing else in common.
+// Weight-streaming FP16 x 4-bit(codebook) GEMM for small token counts (n <= 32
+// per pass) on sm_100a: the memory-bound regime every row of the reference's
+// README table is measured in.  Counterpart of the reference's Tuna<> kernel and
+// its Deq4GemmIterator main loop (kernel.cu:1043-2505, 2816-2960); it keeps the
+// mma orientation (weights are the m16 "A" operand, tokens the n8 "B" operand,
+// kernel.cu:2182-2192) and nothing else.
 //
-// Data path.  A lane reads 16 packed bytes with one streaming 128-bit load:
-// half of an 8x8 tile = 4 rows x 8 columns of one row group.  Lane (g,t)
-// (g = lane/4, t = lane%4) takes row group g/2, rows 4(g%2)..+3, tile 4*step+t,
-// so a warp load covers four 128-byte runs (4 row groups x 4 tiles) = 32 rows x
-// 32 columns.  Each 32-bit word is one row's 8 consecutive columns and becomes
-// the A fragments of two m16n8k16 mma.sync (the k index of an mma is only a
-// label: slot 2t,2t+1 <-> columns 0,1 of tile t, slot 2t+8,+9 <-> columns 2,3;
-// the B fragment is gathered with the same labelling, 16 contiguous bytes of x
-// per lane).  Rows 4g, 4g+1 feed tile "P0", rows 4g+2, 4g+3 tile "P1".
+// Why mma.sync here and not tcgen05: on B200 a tcgen05.mma with M=128, K=16 takes
+// ~128 clocks whatever N is, i.e. at most 16 weights per clock per SM, a third of
+// what HBM delivers; mma.sync.m16n8k16 sustains ~990 MAC/clk/SM = 62 weights per
+// clock at 16 tokens.  The tensor-memory kernel takes over for large token counts.
 //
-// Dequantisation.  A byte holds two codes; a 256-entry byte -> half2 table of
-// fp16(code[hi]), fp16(code[lo]) is replicated once per lane (bank) in shared
-// memory so every lookup is conflict free.  The per-row scale is applied once,
-// in fp32, to the accumulated sum in the epilogue (absmax is constant along K:
-// one block per row, test.py:81, kernel.cu:2178-2180).
+// Structure.  One persistent CTA per SM: warp 0 is a TMA producer, 16 consumer warps
+// arranged warps_m x warps_k.  A "unit" is (row tile of 32*R*warps_m rows, K chunk of
+// 32*S*warps_k columns).  Per unit the producer brings in, through an mbarrier ring,
+//   * the packed weights: warps_k boxes of [4*R*warps_m row groups] x [128*S bytes] from the
+//     [m/8] x [4k] byte view of q (one row group = 8 rows = 4k contiguous bytes, test.py:58-65);
+//   * the activations: warps_k boxes of [tile_tok tokens] x [32*S columns] fp16.
+// A consumer lane reads 16 packed bytes (half an 8x8 tile: 4 rows x 8 columns) with one
+// 128-bit shared load; lane (g,t) takes row group g/2, rows 4(g%2)..+3, tile t of the four
+// tiles of a 32-column step.  Each 32-bit word is 8 consecutive columns of one row and
+// becomes the A fragments of two m16n8k16 (the k index of an mma is a label: slots 2t,2t+1
+// <-> columns 0,1 of tile t, slots 2t+8,+9 <-> columns 2,3; the B fragment is the matching
+// 16 contiguous bytes of x).  Rows 4g, 4g+1 feed accumulator tile P0, rows 4g+2, 4g+3 tile P1.
 //
-// Split-K.  Warps of a CTA that share rows reduce through shared memory in a
-// fixed order.  CTAs along K write fp32 partials to the workspace; the CTA that
-// arrives last at the tile's counter adds them in split order, so the result
-// does not depend on arrival order, the output needs no zero fill and there
-// are no floating-point atomics (the reference atomically adds fp16 partials,
-// kernel.cu:2739-2745).
+// Dequantisation: a byte holds two codes; a 256-entry byte -> half2(fp16(code[hi]),
+// fp16(code[lo])) table is replicated once per bank (entry stride 256 bytes) at a
+// 64-KB-aligned shared address, so that ONE prmt builds the whole address
+// (0x10000*j | byte << 8 | lane*4) and every lookup is conflict free.  The per-row scale
+// is constant along K (one block per row, test.py:81, kernel.cu:2178-2180) and is applied
+// once, in fp32, to the accumulated sum.
+//
+// Split-K: units are numbered tile-major and cut into one contiguous range per CTA
+// ("stream-K"), so every SM streams the same number of bytes.  Warps that share rows
+// reduce through shared memory in a fixed tree; a tile cut across CTAs is finished by the
+// CTA that arrives last at the tile's counter, which adds the fp32 partials from the
+// workspace in unit order.  Results are bit-identical from run to run, the output needs no
+// zero fill, and there are no floating-point atomics (the reference atomically adds fp16
+// partials, kernel.cu:2739-2745).
+//
+// Every wait is bounded (see sm100_ptx.cuh): a wait that runs out records where, raises
+// the CTA's abort flag and everybody unwinds to the common exit.
+#include <cstring>
+#include <mutex>
 #include "common.cuh"
 #include "launchers.h"
+#include "sm100_ptx.cuh"
 
 namespace tuna {
 
-constexpr int kLutBytes = 256 * 32 * 4;  // 256 entries x 32 lane copies x half2
-constexpr int kStreamMaxSmem = 200 * 1024;
-constexpr int kPrefetch = 2;  // k-steps of weight loads in flight per warp
+constexpr int kConsumerWarps = 16;
+constexpr int kStreamThreads = 32 * (1 + kConsumerWarps);
+constexpr int kLut64Bytes = 65536;           // 256 entries x 256-byte stride (32 lanes x 4 bytes used)
+constexpr int kStreamSmemLimit = 227 * 1024 - 2048;  // dynamic request; static barriers take the rest
+constexpr int S_MAX = 2;                     // 32-column steps per warp per unit, at most
 
 struct StreamParams {
-    const uint8_t *q;
-    const __half *x;
     const float *code;
     const float *absmax;
     __half *o;
-    float *partials;        // workspace: split-K partial tiles
-    unsigned int *counters; // workspace: one per row tile, zero between calls
+    float *partials;
+    unsigned int *counters;
+    DeviceStatus *status;
     int m, n, k;
-    int tok0;               // first token of this pass
-    int warps_m, warps_k, split_k;
-    int steps_total;        // ceil(k / 32)
-    int x_stride_bytes;     // shared-memory row pitch of the x slice
-    int max_cta_steps;
+    int tok0;          // first token of this pass
+    int warps_m, warps_k;
+    int ksteps;        // S: 32-column steps per warp per unit
+    int stages;
+    int row_tiles, chunks;
+    long long units;
+    int stage_w_bytes, stage_x_bytes;
+    int red_bytes;     // shared-memory scratch of the in-CTA reduction
 };
 
 __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -61,143 +82,121 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Even split of `total` items over `parts`: [begin, end) of part `i`.
-__host__ __device__ inline void even_split(int total, int parts, int i, int &begin, int &end)
+__device__ __forceinline__ uint32_t lut_lookup(uint32_t w, uint32_t lane_key, uint32_t selector)
 {
-    begin = (int)(((long long)total * i) / parts);
-    end = (int)(((long long)total * (i + 1)) / parts);
+    // result bytes: [0] = lane*4, [1] = the selected byte of w, [2..3] = upper address bytes
+    uint32_t addr, v;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(addr) : "r"(w), "r"(lane_key), "r"(selector));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
 }
 
 template <int R, int NT>
-__global__ void __launch_bounds__(512, 1) gemm_stream_kernel(const StreamParams p)
+__global__ void __launch_bounds__(kStreamThreads, 1)
+gemm_stream_kernel(const StreamParams p, const __grid_constant__ CUtensorMap tmap_q,
+                   const __grid_constant__ CUtensorMap tmap_x)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint32_t *lut = reinterpret_cast<uint32_t *>(smem);
-    uint8_t *xs = smem + kLutBytes;
-    __shared__ unsigned int s_ticket;
+    __shared__ __align__(8) uint64_t bars[40];
+    __shared__ int s_abort;
+    __shared__ int s_last;
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int wm = warp % p.warps_m, wk = warp / p.warps_m;
-    const int tile_rows = 32 * R * p.warps_m;
-    const int row_tile = blockIdx.x;
-    const int split = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cta = blockIdx.x, ctas = gridDim.x;
+    const int WM = p.warps_m, WK = p.warps_k, S = p.ksteps;
+    volatile int *abort_flag = &s_abort;
 
-    int cta_s0, cta_s1;
-    even_split(p.steps_total, p.split_k, split, cta_s0, cta_s1);
+    // Shared-memory map: the table sits at the first 64-KB boundary; stage buffers fill the
+    // space before it (if a whole stage fits) and after it; reduction scratch last.
+    const uint32_t base = smem_u32(smem);
+    const uint32_t lut_addr = (base + 0xFFFFu) & ~0xFFFFu;
+    const uint32_t stage_bytes = (uint32_t)(p.stage_w_bytes + p.stage_x_bytes);
+    uint32_t dyn_bytes;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    const int stages_before = (int)((lut_addr - base) / stage_bytes);
+    // the ring is as deep as asked for, or as deep as the space around the table allows
+    const int room_after = (int)(((long long)base + dyn_bytes - (long long)lut_addr - kLut64Bytes - p.red_bytes) / (long long)stage_bytes);
+    const int NS = min(p.stages, stages_before + max(room_after, 0));
+    auto stage_addr = [&](int s) -> uint32_t {
+        return s < stages_before ? base + (uint32_t)s * stage_bytes
+                                 : lut_addr + kLut64Bytes + (uint32_t)(s - stages_before) * stage_bytes;
+    };
+    const int stages_after = NS > stages_before ? NS - stages_before : 0;
+    const uint32_t red_addr = lut_addr + kLut64Bytes + (uint32_t)stages_after * stage_bytes;
 
-    // ---- byte -> half2 table, one copy per bank
-    for (int e = warp; e < 256; e += blockDim.x >> 5) {
+    const uint32_t bar0 = smem_u32(&bars[0]);
+    const uint32_t full = bar0, empty = bar0 + 8 * NS, sync_bar = bar0 + 16 * NS;
+
+    if (NS < 2 || room_after < 0) {  // cannot happen with the launcher's request; never run without a ring
+        if (threadIdx.x == 0 && atomicCAS(&p.status->code, 0, 20) == 0) p.status->detail = NS;
+        return;
+    }
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        s_last = 0;
+        for (int i = 0; i < NS; ++i) { mbar_init(full + 8 * i, 1); mbar_init(empty + 8 * i, kConsumerWarps); }
+        mbar_init(sync_bar, kConsumerWarps);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // byte -> half2 table: even column = high nibble in the low half; 32 copies, one per bank
+    for (int e = warp; e < 256; e += kStreamThreads / 32) {
         const __half hi = __float2half_rn(p.code[e >> 4]);
         const __half lo = __float2half_rn(p.code[e & 15]);
-        lut[e * 32 + lane] = (uint32_t)__half_as_ushort(hi) | ((uint32_t)__half_as_ushort(lo) << 16);
-    }
-    // ---- x slice [NT*8 tokens][32*(s1-s0) columns], zero where token >= n or column >= k
-    {
-        const int cols = (cta_s1 - cta_s0) * 32;
-        const int chunks_per_row = cols / 8;  // 16-byte chunks
-        const int total = NT * 8 * chunks_per_row;
-        for (int i = tid; i < total; i += blockDim.x) {
-            const int row = i / chunks_per_row, c = i - row * chunks_per_row;
-            const int tok = p.tok0 + row, col = cta_s0 * 32 + c * 8;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (tok < p.n && col < p.k)  // k % 8 == 0: a chunk is all in or all out
-                v = *reinterpret_cast<const uint4 *>(p.x + (size_t)tok * p.k + col);
-            *reinterpret_cast<uint4 *>(xs + (size_t)row * p.x_stride_bytes + c * 16) = v;
-        }
+        const uint32_t v = (uint32_t)__half_as_ushort(hi) | ((uint32_t)__half_as_ushort(lo) << 16);
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(lut_addr + (uint32_t)e * 256 + lane * 4), "r"(v) : "memory");
     }
     __syncthreads();
 
-    // ---- this warp's rows and k-steps
-    int s0, s1;
-    even_split(cta_s1 - cta_s0, p.warps_k, wk, s0, s1);
-    s0 += cta_s0;
-    s1 += cta_s0;
-    const int warp_row0 = row_tile * tile_rows + wm * 32 * R;
-    const int n_rg = p.m >> 3, n_kt = p.k >> 3;
+    // this CTA's contiguous range of units
+    long long u = (p.units * cta) / ctas;
+    const long long u_end = (p.units * (cta + 1)) / ctas;
+    int tile = (int)(u / p.chunks);
+    int chunk = (int)(u - (long long)tile * p.chunks);
+    PROF_ROLE_BEGIN();
 
-    const uint8_t *src[R];
-    bool row_ok[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int rg = (warp_row0 + 32 * r) / 8 + (g >> 1);
-        row_ok[r] = rg < n_rg;
-        src[r] = p.q + (size_t)(row_ok[r] ? rg : 0) * row_group_bytes(p.k) + (size_t)t * 32 + (g & 1) * 16;
-    }
-
-    float acc[R][2][NT][4];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int P = 0; P < 2; ++P)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) acc[r][P][nt][c] = 0.f;
-
-    auto load_step = [&](int s, uint4 (&dst)[R]) {
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            if (s < s1 && row_ok[r] && (4 * s + t) < n_kt)
-                dst[r] = ldg_stream_u4(src[r] + (size_t)s * 128);
-            else
-                dst[r] = make_uint4(0, 0, 0, 0);
-        }
-    };
-
-    uint4 buf[kPrefetch][R];
-#pragma unroll
-    for (int j = 0; j < kPrefetch; ++j) load_step(s0 + j, buf[j]);
-
-    const uint32_t *lut_lane = lut + lane;
-    const uint8_t *xs_lane = xs + (size_t)g * p.x_stride_bytes + t * 16;
-
-    for (int sb = s0; sb < s1; sb += kPrefetch) {
-#pragma unroll
-        for (int j = 0; j < kPrefetch; ++j) {
-            const int s = sb + j;
-            if (s < s1) {
-                uint4 cur[R];
-#pragma unroll
-                for (int r = 0; r < R; ++r) cur[r] = buf[j][r];
-                load_step(s + kPrefetch, buf[j]);
-
-                uint4 xb[NT];
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-                    xb[nt] = *reinterpret_cast<const uint4 *>(
-                        xs_lane + (size_t)(8 * nt) * p.x_stride_bytes + (size_t)(s - cta_s0) * 64);
-
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const uint32_t w[4] = {cur[r].x, cur[r].y, cur[r].z, cur[r].w};
-#pragma unroll
-                    for (int P = 0; P < 2; ++P) {
-                        const uint32_t wa = w[2 * P], wb = w[2 * P + 1];
-                        uint32_t a[8];
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            a[2 * b] = lut_lane[((wa >> (8 * b)) & 0xffu) * 32];
-                            a[2 * b + 1] = lut_lane[((wb >> (8 * b)) & 0xffu) * 32];
-                        }
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            mma_m16n8k16(acc[r][P][nt], a[0], a[1], a[2], a[3], xb[nt].x, xb[nt].y);
-                            mma_m16n8k16(acc[r][P][nt], a[4], a[5], a[6], a[7], xb[nt].z, xb[nt].w);
-                        }
-                    }
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            Ring r;
+            const int rg_per_tile = 4 * R * WM;
+            for (; u < u_end; ++u, r.advance(NS)) {
+                if (!mbar_wait(empty + 8 * r.idx, r.phase ^ 1, abort_flag, p.status, 1)) break;
+                const uint32_t dst = stage_addr(r.idx);
+                mbar_expect_tx(full + 8 * r.idx, stage_bytes);
+                const int k0 = chunk * 32 * S * WK;  // first column of the unit
+                for (int wk = 0; wk < WK; ++wk) {
+                    // byte coordinate inside a row group: 4 bytes per column
+                    tma_load_2d(dst + (uint32_t)wk * (uint32_t)(rg_per_tile * 128 * S), &tmap_q, (k0 + wk * 32 * S) * 4,
+                                tile * rg_per_tile, full + 8 * r.idx);
+                    tma_load_2d(dst + (uint32_t)p.stage_w_bytes + (uint32_t)wk * (uint32_t)(NT * 8 * 64 * S), &tmap_x,
+                                k0 + wk * 32 * S, p.tok0, full + 8 * r.idx);
                 }
+                if (++chunk == p.chunks) { chunk = 0; ++tile; }
             }
         }
-    }
+    } else {
+        // ------------------------------------------------------------------ consumers
+        const int cw = warp - 1;
+        const int wm = cw % WM, wk = cw / WM;
+        const int g = lane >> 2, t = lane & 3;
+        const bool active = wk < WK;  // warps beyond warps_m * warps_k only take part in the barriers
+        const uint32_t lane_key = (lut_addr & 0xFFFF0000u) | (uint32_t)(lane * 4);
+        // offsets of this lane's 16 bytes inside a stage
+        const uint32_t w_box_bytes = (uint32_t)(4 * R * WM * 128 * S);
+        const uint32_t w_off = (uint32_t)wk * w_box_bytes + (uint32_t)(4 * wm * R + (g >> 1)) * (uint32_t)(128 * S) +
+                               (uint32_t)t * 32 + (uint32_t)(g & 1) * 16;
+        const uint32_t x_off = (uint32_t)p.stage_w_bytes + (uint32_t)wk * (uint32_t)(NT * 8 * 64 * S) +
+                               (uint32_t)g * (uint32_t)(64 * S) + (uint32_t)t * 16;
 
-    // ---- reduce the warps that share rows (fixed order: wk = 0, 1, 2, ...)
-    constexpr int kAccRegs = R * 2 * NT * 4;
-    if (p.warps_k > 1) {
-        __syncthreads();  // everyone is done with the x slice; reuse it
-        float *red = reinterpret_cast<float *>(xs);
-        if (wk > 0) {
-            float *dst = red + ((size_t)((wk - 1) * p.warps_m + wm) * kAccRegs) * 32 + lane;
+        float acc[R][2][NT][4];
+        auto zero_acc = [&]() {
 #pragma unroll
             for (int r = 0; r < R; ++r)
 #pragma unroll
@@ -205,161 +204,265 @@ __global__ void __launch_bounds__(512, 1) gemm_stream_kernel(const StreamParams 
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                        for (int c = 0; c < 4; ++c)
-                            dst[(((r * 2 + P) * NT + nt) * 4 + c) * 32] = acc[r][P][nt][c];
-        }
-        __syncthreads();
-        if (wk == 0) {
-            for (int j = 1; j < p.warps_k; ++j) {
-                const float *srcp = red + ((size_t)((j - 1) * p.warps_m + wm) * kAccRegs) * 32 + lane;
-#pragma unroll
-                for (int r = 0; r < R; ++r)
-#pragma unroll
-                    for (int P = 0; P < 2; ++P)
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                            for (int c = 0; c < 4; ++c)
-                                acc[r][P][nt][c] += srcp[(((r * 2 + P) * NT + nt) * 4 + c) * 32];
-            }
-        }
-    }
+                        for (int c = 0; c < 4; ++c) acc[r][P][nt][c] = 0.f;
+        };
+        constexpr int kAccRegs = R * 2 * NT * 4;
+        float *accf = &acc[0][0][0][0];
+        uint32_t sync_phase = 0;
+        // bounded rendezvous of the 16 consumer warps
+        auto consumers_sync = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sync_bar);
+            const bool ok = mbar_wait(sync_bar, sync_phase & 1, abort_flag, p.status, 3);
+            ++sync_phase;
+            return ok;
+        };
 
-    // ---- reduce the CTAs along K through the workspace (last arriver sums in split order)
-    if (p.split_k > 1) {
-        const size_t tile_floats = (size_t)p.warps_m * kAccRegs * 32;
-        float *tile_base = p.partials + (size_t)row_tile * p.split_k * tile_floats;
-        if (wk == 0) {
-            float *dst = tile_base + (size_t)split * tile_floats + (size_t)wm * kAccRegs * 32 + lane;
+        Ring r;
+        bool ok = true;
+        while (ok && u < u_end) {
+            // ---- one segment: the units of one tile inside this CTA's range
+            const int seg_tile = tile, c0 = chunk;
+            const long long left = u_end - u;
+            const int c1 = (int)((long long)(p.chunks - c0) <= left ? p.chunks : c0 + left);
+            zero_acc();
+            for (int c = c0; c < c1; ++c, r.advance(NS)) {
+                if (!mbar_wait(full + 8 * r.idx, r.phase, abort_flag, p.status, 2)) { ok = false; break; }
+                const uint32_t st = stage_addr(r.idx);
+                uint4 wv[S_MAX][R];
+                uint4 xv[S_MAX][NT];
 #pragma unroll
-            for (int i = 0; i < kAccRegs; ++i)
-                dst[i * 32] = (&acc[0][0][0][0])[i];
-        }
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const unsigned int old = atomicAdd(&p.counters[row_tile], 1u);
-            s_ticket = old;
-            if (old == (unsigned)p.split_k - 1) p.counters[row_tile] = 0;  // leave it clean
-        }
-        __syncthreads();
-        if (s_ticket != (unsigned)p.split_k - 1) return;
-        __threadfence();
-        if (wk == 0) {
+                for (int s = 0; s < S_MAX; ++s) {
+                    if (s < S && active) {
 #pragma unroll
-            for (int i = 0; i < kAccRegs; ++i) (&acc[0][0][0][0])[i] = 0.f;
-            for (int s = 0; s < p.split_k; ++s) {
-                const float *srcp = tile_base + (size_t)s * tile_floats + (size_t)wm * kAccRegs * 32 + lane;
+                        for (int rr = 0; rr < R; ++rr) wv[s][rr] = lds128(st + w_off + (uint32_t)rr * (uint32_t)(4 * 128 * S) + s * 128);
 #pragma unroll
-                for (int i = 0; i < kAccRegs; ++i)
-                    (&acc[0][0][0][0])[i] += __ldcg(srcp + i * 32);
+                        for (int nt = 0; nt < NT; ++nt) xv[s][nt] = lds128(st + x_off + (uint32_t)nt * (uint32_t)(8 * 64 * S) + s * 64);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty + 8 * r.idx);  // the stage is in registers
+                if (active) {
+#pragma unroll
+                    for (int s = 0; s < S_MAX; ++s) {
+                        if (s < S) {
+#pragma unroll
+                            for (int rr = 0; rr < R; ++rr) {
+                                const uint32_t w[4] = {wv[s][rr].x, wv[s][rr].y, wv[s][rr].z, wv[s][rr].w};
+#pragma unroll
+                                for (int P = 0; P < 2; ++P) {
+                                    const uint32_t wa = w[2 * P], wb = w[2 * P + 1];
+                                    const uint32_t a0 = lut_lookup(wa, lane_key, 0x7604), a1 = lut_lookup(wb, lane_key, 0x7604);
+                                    const uint32_t a2 = lut_lookup(wa, lane_key, 0x7614), a3 = lut_lookup(wb, lane_key, 0x7614);
+                                    const uint32_t a4 = lut_lookup(wa, lane_key, 0x7624), a5 = lut_lookup(wb, lane_key, 0x7624);
+                                    const uint32_t a6 = lut_lookup(wa, lane_key, 0x7634), a7 = lut_lookup(wb, lane_key, 0x7634);
+#pragma unroll
+                                    for (int nt = 0; nt < NT; ++nt) {
+                                        mma_m16n8k16(acc[rr][P][nt], a0, a1, a2, a3, xv[s][nt].x, xv[s][nt].y);
+                                        mma_m16n8k16(acc[rr][P][nt], a4, a5, a6, a7, xv[s][nt].z, xv[s][nt].w);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
             }
-        }
-    }
-    if (wk != 0) return;
+            if (!ok) break;
+            // advance the cursor past this segment
+            u += c1 - c0;
+            chunk = c1;
+            if (chunk == p.chunks) { chunk = 0; ++tile; }
 
-    // ---- epilogue: scale by absmax (fp32), round once to fp16, 8-byte stores of 4 rows
+            // ---- reduce the warps that share rows: fixed binary tree over wk
+            if (WK > 1) {
+                for (int half = 1; half < WK; half <<= 1) {
+                    const bool sender = active && (wk & (2 * half - 1)) == half;
+                    const bool receiver = active && (wk & (2 * half - 1)) == 0 && wk + half < WK;
+                    const uint32_t slot = red_addr + (uint32_t)(((wk >> 1) / half) * WM + wm) * (uint32_t)(kAccRegs * 128) + lane * 4;
+                    if (sender) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int row = warp_row0 + 32 * r + 4 * g;
-        if (row >= p.m) continue;  // m % 8 == 0 and 4 rows sit inside one 8-row group
-        const float4 sc = *reinterpret_cast<const float4 *>(p.absmax + row);
+                        for (int i = 0; i < kAccRegs; ++i)
+                            asm volatile("st.shared.f32 [%0], %1;" ::"r"(slot + i * 128), "f"(accf[i]) : "memory");
+                    }
+                    if (!consumers_sync()) { ok = false; break; }
+                    if (receiver) {
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
+                        for (int i = 0; i < kAccRegs; ++i) {
+                            float v;
+                            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(slot + i * 128));
+                            accf[i] += v;
+                        }
+                    }
+                    if (!consumers_sync()) { ok = false; break; }
+                }
+                if (!ok) break;
+            }
+
+            // ---- a tile cut across CTAs: partials through the workspace, last arriver sums
+            const bool full_tile = (c0 == 0 && c1 == p.chunks);
+            bool do_store = full_tile;
+            if (!full_tile) {
+                const size_t tile_floats = (size_t)WM * kAccRegs * 32;
+                if (active && wk == 0) {
+                    float *dst = p.partials + (size_t)(2 * cta + (c0 == 0 ? 1 : 0)) * tile_floats + (size_t)wm * kAccRegs * 32 + lane;
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {  // token 2t + e
-                const int tok = p.tok0 + nt * 8 + 2 * t + e;
-                if (tok >= p.n) continue;
-                uint2 v;
-                v.x = pack_half2(acc[r][0][nt][e] * sc.x, acc[r][0][nt][2 + e] * sc.y);
-                v.y = pack_half2(acc[r][1][nt][e] * sc.z, acc[r][1][nt][2 + e] * sc.w);
-                *reinterpret_cast<uint2 *>(p.o + (size_t)tok * p.m + row) = v;
+                    for (int i = 0; i < kAccRegs; ++i) dst[i * 32] = accf[i];
+                }
+                __threadfence();
+                if (!consumers_sync()) break;
+                const int cta_first = cta_of_unit((long long)seg_tile * p.chunks, p.units, ctas);
+                const int cta_last = cta_of_unit((long long)(seg_tile + 1) * p.chunks - 1, p.units, ctas);
+                const int nseg = cta_last - cta_first + 1;
+                if (cw == 0 && lane == 0) {
+                    const unsigned int old = atomicAdd(&p.counters[seg_tile], 1u);
+                    const int is_last = (old == (unsigned)nseg - 1);
+                    if (is_last) p.counters[seg_tile] = 0;  // leave the counter clean for the next call
+                    s_last = is_last;
+                }
+                if (!consumers_sync()) break;
+                const int is_last = s_last;
+                if (!consumers_sync()) break;  // s_last may be rewritten by the next segment
+                if (is_last) {
+                    __threadfence();
+                    if (active && wk == 0) {
+#pragma unroll
+                        for (int i = 0; i < kAccRegs; ++i) accf[i] = 0.f;
+                        for (int s = 0; s < nseg; ++s) {
+                            const float *src = p.partials + (size_t)(2 * (cta_first + s) + (s == 0 ? 1 : 0)) * tile_floats +
+                                               (size_t)wm * kAccRegs * 32 + lane;
+#pragma unroll
+                            for (int i = 0; i < kAccRegs; ++i) accf[i] += __ldcg(src + i * 32);
+                        }
+                    }
+                    do_store = true;
+                }
+            }
+
+            // ---- epilogue: fp32 scale by absmax, one rounding to fp16, 8-byte stores of 4 rows
+            if (do_store && active && wk == 0) {
+#pragma unroll
+                for (int rr = 0; rr < R; ++rr) {
+                    const int row = seg_tile * 32 * R * WM + (wm * R + rr) * 32 + 4 * g;
+                    if (row >= p.m) continue;  // m % 8 == 0 and the 4 rows sit inside one 8-row group
+                    const float4 sc = *reinterpret_cast<const float4 *>(p.absmax + row);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {  // token 2t + e
+                            const int tok = p.tok0 + nt * 8 + 2 * t + e;
+                            if (tok >= p.n) continue;
+                            uint2 v;
+                            v.x = pack_half2(acc[rr][0][nt][e] * sc.x, acc[rr][0][nt][2 + e] * sc.y);
+                            v.y = pack_half2(acc[rr][1][nt][e] * sc.z, acc[rr][1][nt][2 + e] * sc.w);
+                            *reinterpret_cast<uint2 *>(p.o + (size_t)tok * p.m + row) = v;
+                        }
+                    }
+                }
             }
         }
     }
+    PROF_ROLE_END(warp == 0 ? 0 : 1);
 }
 
 // ------------------------------------------------------------------ host side
 
-static int stream_x_stride_bytes(int cta_steps)
+static void stream_geometry(int m, int k, const tuna_config &c, int nt, StreamParams *p)
 {
-    int b = cta_steps * 64;
-    if (b % 128 == 0) b += 64;  // rows g and g+1 must land in different bank halves
-    return b;
+    p->warps_m = c.warps_m; p->warps_k = c.warps_k; p->ksteps = c.k_steps; p->stages = c.stages_w;
+    const int tile_rows = 32 * c.rows_per_warp * c.warps_m;
+    const int chunk_cols = 32 * c.k_steps * c.warps_k;
+    p->row_tiles = div_up(m, tile_rows);
+    p->chunks = div_up(k, chunk_cols);
+    p->units = (long long)p->row_tiles * p->chunks;
+    p->stage_w_bytes = tile_rows * chunk_cols / 2;
+    p->stage_x_bytes = nt * 8 * chunk_cols * 2;
+    const int acc_regs = c.rows_per_warp * 2 * nt * 4;
+    p->red_bytes = c.warps_k > 1 ? (c.warps_k / 2) * c.warps_m * acc_regs * 128 : 0;
 }
 
-static size_t stream_smem_bytes(const tuna_config &c, int steps_total, int nt)
+// The kernel lays its buffers out around the first 64-KB boundary of its own shared window and
+// takes as many stages as fit (at most `stages_w`); the launcher always asks for the whole SM.
+// This is the lower bound that guarantees two stages wherever that boundary falls.
+static size_t stream_min_smem_bytes(const StreamParams &p)
 {
-    const int max_cta_steps = div_up(steps_total, c.split_k);
-    const size_t xbytes = (size_t)nt * 8 * stream_x_stride_bytes(max_cta_steps);
-    const size_t red = (size_t)(c.warps_k - 1) * c.warps_m * (c.rows_per_warp * 2 * nt * 4) * 32 * 4;
-    return kLutBytes + (xbytes > red ? xbytes : red);
+    const size_t stage = (size_t)p.stage_w_bytes + p.stage_x_bytes;
+    return 4096 + kLut64Bytes + 2 * stage + p.red_bytes + (65536 - 4096) % stage;
 }
 
 int gemm_stream_normalize_config(int m, int n, int k, int sm_count, tuna_config *c)
 {
-    if (c->tile_tok == 0) c->tile_tok = (n <= 8) ? 8 : 16;
-    if (c->tile_tok != 8 && c->tile_tok != 16) return TUNA_ERR_BAD_CONFIG;
+    if (c->tile_tok == 0) c->tile_tok = (n <= 8) ? 8 : (n <= 16 ? 16 : 32);
+    if (c->tile_tok != 8 && c->tile_tok != 16 && c->tile_tok != 32) return TUNA_ERR_BAD_CONFIG;
     const int nt = c->tile_tok / 8;
-    const int steps_total = div_up(k, 32);
-    const bool heuristic = c->rows_per_warp == 0 || c->warps_m == 0 || c->warps_k == 0 || c->split_k == 0;
-    if (heuristic) {
-        // One CTA of 16 warps per SM.  Pick the row tile so that tiles x split_k lands just
-        // under a multiple of the SM count, and keep >= ~8 k-steps per warp.
-        const int blocks = div_up(m, 32);
-        int best_r = 1, best_wm = 1, best_wk = 16, best_sk = 1;
-        double best_cost = 1e30;
-        for (int r : {1, 2, 4})
-            for (int wmv : {1, 2, 4, 8, 16})
-                for (int sk = 1; sk <= 32; ++sk) {
-                    const int wkv = 16 / wmv;
-                    if (steps_total / sk < 1) continue;
+    if (c->stages_w == 0) c->stages_w = 12;  // an upper bound: the kernel takes what fits
+    if (c->ctas < 0) return TUNA_ERR_BAD_CONFIG;
+    if (c->ctas == 0 || c->ctas > sm_count) c->ctas = sm_count;
+    StreamParams p;
+    if (c->rows_per_warp == 0 || c->warps_m == 0 || c->warps_k == 0 || c->k_steps == 0) {
+        // No table entry: pick the geometry with the least estimated traffic.  Weights are read
+        // once whatever the geometry; what differs is the activation re-reads (one x box per
+        // unit, from L2) and the split-K partials (written and read back once per cut tile).
+        double best = 1e300;
+        tuna_config bc = *c;
+        for (int r = 1; r <= 2; ++r)
+            for (int wm = 1; wm <= 16; wm <<= 1)
+                for (int ks = 1; ks <= 2; ++ks) {
                     tuna_config t = *c;
-                    t.rows_per_warp = r; t.warps_m = wmv; t.warps_k = wkv; t.split_k = sk;
-                    if (stream_smem_bytes(t, steps_total, nt) > (size_t)kStreamMaxSmem) continue;
-                    const int tiles = div_up(blocks, r * wmv);
-                    const long long ctas = (long long)tiles * sk;
-                    const int waves = (int)div_up_ll(ctas, sm_count);
-                    // time ~ waves x (work per CTA) + fixed costs; work per CTA ~ r*wmv*steps/sk
-                    const double steps_per_warp = (double)steps_total / sk / wkv;
-                    double cost = waves * ((double)r * wmv * steps_total / sk + 400.0)
-                                  + (sk > 1 ? 300.0 : 0.0) + 8.0 * wkv
-                                  + (steps_per_warp < 4 ? 400.0 : 0.0)
-                                  + 64.0 / r;  // B-fragment re-reads
-                    if (cost < best_cost) { best_cost = cost; best_r = r; best_wm = wmv; best_wk = wkv; best_sk = sk; }
+                    t.rows_per_warp = c->rows_per_warp ? c->rows_per_warp : r;
+                    t.warps_m = c->warps_m ? c->warps_m : wm;
+                    t.warps_k = c->warps_k ? c->warps_k : 16 / t.warps_m;
+                    t.k_steps = c->k_steps ? c->k_steps : ks;
+                    while (t.warps_k > 1 && 32 * t.k_steps * (t.warps_k / 2) >= k) t.warps_k >>= 1;
+                    if (t.rows_per_warp * nt > 4 || t.warps_m * t.warps_k > kConsumerWarps) continue;
+                    stream_geometry(m, k, t, nt, &p);
+                    if (stream_min_smem_bytes(p) > (size_t)kStreamSmemLimit) continue;
+                    const double x_bytes = (double)p.units * p.stage_x_bytes;
+                    const double tile_bytes = (double)t.warps_m * t.rows_per_warp * 32 * nt * 8 * 4;
+                    const double cuts = (p.units % c->ctas == 0 && p.chunks % (p.units / c->ctas) == 0) ? 0 : 2.0 * c->ctas;
+                    const double ring = (double)(kStreamSmemLimit - 70000 - p.red_bytes) / (p.stage_w_bytes + p.stage_x_bytes);
+                    double cost = 0.5 * x_bytes + 3.0 * cuts * tile_bytes + (ring < 3 ? 1e12 : 0) +
+                                  (t.warps_k > 1 ? 2e5 * t.warps_k : 0);
+                    if (cost < best) { best = cost; bc = t; }
                 }
-        c->rows_per_warp = best_r; c->warps_m = best_wm; c->warps_k = best_wk; c->split_k = best_sk;
+        if (best >= 1e300) return TUNA_ERR_BAD_CONFIG;
+        *c = bc;
     }
-    if (c->rows_per_warp != 1 && c->rows_per_warp != 2 && c->rows_per_warp != 4) return TUNA_ERR_BAD_CONFIG;
-    if (c->warps_m < 1 || c->warps_k < 1 || c->warps_m * c->warps_k > 16) return TUNA_ERR_BAD_CONFIG;
-    if (c->split_k < 1 || c->split_k > steps_total) return TUNA_ERR_BAD_CONFIG;
-    if (stream_smem_bytes(*c, steps_total, nt) > (size_t)kStreamMaxSmem) return TUNA_ERR_BAD_CONFIG;
+    auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
+    if (c->rows_per_warp != 1 && c->rows_per_warp != 2) return TUNA_ERR_BAD_CONFIG;
+    if (c->rows_per_warp * nt > 4) return TUNA_ERR_BAD_CONFIG;  // accumulator registers
+    if (c->k_steps != 1 && c->k_steps != 2) return TUNA_ERR_BAD_CONFIG;
+    if (!pow2(c->warps_m) || !pow2(c->warps_k) || c->warps_m * c->warps_k > kConsumerWarps) return TUNA_ERR_BAD_CONFIG;
+    if (4 * c->rows_per_warp * c->warps_m > 256) return TUNA_ERR_BAD_CONFIG;
+    if (c->stages_w < 2 || c->stages_w > 16) return TUNA_ERR_BAD_CONFIG;
+    stream_geometry(m, k, *c, nt, &p);
+    if (stream_min_smem_bytes(p) > (size_t)kStreamSmemLimit) return TUNA_ERR_BAD_CONFIG;
     (void)n;
     return TUNA_OK;
 }
 
 size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &c)
 {
-    (void)n; (void)k;
+    (void)n;
+    StreamParams p;
     const int nt = c.tile_tok / 8;
-    const int tiles = div_up(m, 32 * c.rows_per_warp * c.warps_m);
-    const size_t counters = ((size_t)tiles * 4 + 255) / 256 * 256;
-    if (c.split_k <= 1) return counters;
+    stream_geometry(m, k, c, nt, &p);
+    const size_t counters = ((size_t)p.row_tiles * 4 + 255) / 256 * 256;
     const size_t tile_floats = (size_t)c.warps_m * (c.rows_per_warp * 2 * nt * 4) * 32;
-    return counters + (size_t)tiles * c.split_k * tile_floats * 4;
+    return counters + 2 * (size_t)c.ctas * tile_floats * 4;
 }
 
 template <int R, int NT>
-static int launch_one(const StreamParams &p, dim3 grid, int threads, size_t smem, cudaStream_t stream)
+static int launch_one(const StreamParams &p, const CUtensorMap &mq, const CUtensorMap &mx, int ctas, size_t smem,
+                      cudaStream_t stream)
 {
     static bool attr_set = false;  // one-time opt-in to large dynamic shared memory
     if (!attr_set) {
         if (cudaFuncSetAttribute(gemm_stream_kernel<R, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kStreamMaxSmem) != cudaSuccess)
+                                 kStreamSmemLimit) != cudaSuccess)
             return TUNA_ERR_NO_DEVICE;
         attr_set = true;
     }
-    gemm_stream_kernel<R, NT><<<grid, threads, smem, stream>>>(p);
+    gemm_stream_kernel<R, NT><<<ctas, kStreamThreads, smem, stream>>>(p, mq, mx);
     return cudaGetLastError() == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
 }
 
@@ -367,33 +470,41 @@ int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)
 {
     const int nt = cfg.tile_tok / 8;
     StreamParams p;
-    p.q = a.q; p.x = (const __half *)a.x; p.code = a.code; p.absmax = a.absmax; p.o = (__half *)a.o;
+    std::memset(&p, 0, sizeof(p));
+    p.code = a.code; p.absmax = a.absmax; p.o = (__half *)a.o;
     p.m = a.m; p.n = a.n; p.k = a.k;
-    p.warps_m = cfg.warps_m; p.warps_k = cfg.warps_k; p.split_k = cfg.split_k;
-    p.steps_total = div_up(a.k, 32);
-    p.max_cta_steps = div_up(p.steps_total, cfg.split_k);
-    p.x_stride_bytes = stream_x_stride_bytes(p.max_cta_steps);
-    const int tiles = div_up(a.m, 32 * cfg.rows_per_warp * cfg.warps_m);
-    const size_t counters = ((size_t)tiles * 4 + 255) / 256 * 256;
-    const size_t need = gemm_stream_workspace_bytes(a.m, a.n, a.k, cfg);
-    if (cfg.split_k > 1 && (a.workspace == nullptr || a.workspace_bytes < need)) return TUNA_ERR_WORKSPACE;
+    stream_geometry(a.m, a.k, cfg, nt, &p);
+    p.status = device_status_word();
+    if (!p.status) return TUNA_ERR_NO_DEVICE;
+    const size_t counters = ((size_t)p.row_tiles * 4 + 255) / 256 * 256;
+    if (a.workspace == nullptr || a.workspace_bytes < gemm_stream_workspace_bytes(a.m, a.n, a.k, cfg))
+        return TUNA_ERR_WORKSPACE;
     p.counters = (unsigned int *)a.workspace;
-    p.partials = a.workspace ? (float *)((uint8_t *)a.workspace + counters) : nullptr;
-    const size_t smem = stream_smem_bytes(cfg, p.steps_total, nt);
-    const dim3 grid(tiles, cfg.split_k);
-    const int threads = 32 * cfg.warps_m * cfg.warps_k;
+    p.partials = (float *)((uint8_t *)a.workspace + counters);
+    int ctas = cfg.ctas;
+    if ((long long)ctas > p.units) ctas = (int)p.units;
+
+    CUtensorMap mq, mx;
+    // packed weights as [m/8 row groups][4k bytes]; box = tile's row groups x (128 * S) bytes
+    if (!make_tensor_map_2d(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.q, (uint64_t)a.k * 4, (uint64_t)a.m / 8,
+                            (uint64_t)a.k * 4, 128u * cfg.k_steps, 4u * cfg.rows_per_warp * cfg.warps_m,
+                            CU_TENSOR_MAP_SWIZZLE_NONE))
+        return TUNA_ERR_NO_DEVICE;
+    // activations as [n][k] fp16; box = tile_tok tokens x (32 * S) columns
+    if (!make_tensor_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.x, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.k * 2,
+                            32u * cfg.k_steps, (uint32_t)cfg.tile_tok, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return TUNA_ERR_NO_DEVICE;
+    const size_t smem = kStreamSmemLimit;
 
     for (int tok0 = 0; tok0 < a.n; tok0 += cfg.tile_tok) {
         p.tok0 = tok0;
         int st;
-        const int key = cfg.rows_per_warp * 10 + nt;
-        switch (key) {
-            case 11: st = launch_one<1, 1>(p, grid, threads, smem, a.stream); break;
-            case 12: st = launch_one<1, 2>(p, grid, threads, smem, a.stream); break;
-            case 21: st = launch_one<2, 1>(p, grid, threads, smem, a.stream); break;
-            case 22: st = launch_one<2, 2>(p, grid, threads, smem, a.stream); break;
-            case 41: st = launch_one<4, 1>(p, grid, threads, smem, a.stream); break;
-            case 42: st = launch_one<4, 2>(p, grid, threads, smem, a.stream); break;
+        switch (cfg.rows_per_warp * 10 + nt) {
+            case 11: st = launch_one<1, 1>(p, mq, mx, ctas, smem, a.stream); break;
+            case 12: st = launch_one<1, 2>(p, mq, mx, ctas, smem, a.stream); break;
+            case 14: st = launch_one<1, 4>(p, mq, mx, ctas, smem, a.stream); break;
+            case 21: st = launch_one<2, 1>(p, mq, mx, ctas, smem, a.stream); break;
+            case 22: st = launch_one<2, 2>(p, mq, mx, ctas, smem, a.stream); break;
             default: return TUNA_ERR_BAD_CONFIG;
         }
         if (st != TUNA_OK) return st;

@@ -1,9 +1,615 @@
-// placeholder until the tcgen05 kernel lands
+// FP16 x 4-bit(codebook) GEMM on the 5th-generation tensor cores (tcgen05) of
+// sm_100a, for every token count.  Counterpart of the reference's Tuna<> kernel
+// and its cp.async / ldmatrix / mma.sync main loop (kernel.cu:1043-2505,
+// 2816-2960); the orientation is kept (weights are MMA operand A, tokens are
+// operand B, the accumulator is an o^T tile, kernel.cu:2182-2192) and nothing
+// else.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      producer   TMA: packed weights ([m/8 row groups] x [4k bytes] viewed as a 2-D
+//                          u8 tensor, 128-byte swizzle) and activation tiles ([n] x [k] fp16,
+//                          128-byte swizzle) into mbarrier-tracked shared-memory rings
+//   warp 1      MMA        one thread issues tcgen05.mma (M=128, N=tile_tok, K=16, fp32
+//                          accumulate): A from TENSOR MEMORY, B through a shared-memory
+//                          descriptor, D in tensor memory
+//   warps 2-5   epilogue   tcgen05.ld of the accumulator, fp32 scale by absmax, fp16 store,
+//                          split-K fix-up
+//   warps 6..   dequant    packed bytes (shared memory) -> byte->half2 table lookups ->
+//                          tcgen05.st into the A-operand slots of tensor memory.  A thread owns
+//                          one weight row (= one TMEM lane): a 32-bit word of the packed layout
+//                          is 8 consecutive columns of one row (test.py:58-65), i.e. four
+//                          32-bit TMEM columns, in K order.
+// The dequantised fp16 weights never touch shared or global memory.  The scale is
+// constant along K (one block per row, test.py:81, kernel.cu:2178-2180), so it is applied
+// once, in fp32, to the accumulated sum.
+//
+// Work decomposition ("stream-K"): a unit is (tile of 128*row_blocks rows x tile_tok tokens,
+// 64-wide K chunk); the units are numbered tile-major and cut into one contiguous range per
+// CTA, so every SM streams the same number of bytes whatever the shape.  A tile cut across
+// CTAs is finished by whichever CTA arrives last at the tile's counter: it adds the fp32
+// partials from the workspace in unit order, so the result does not depend on arrival order
+// (the reference adds fp16 partials with atomicAdd, kernel.cu:2739-2745).  No floating-point
+// atomics, no zero-filled output.
+//
+// Every wait in the kernel is bounded: when a wait runs out the CTA records where in the
+// device status word, raises a CTA-wide abort flag and unwinds to the common exit, where the
+// tensor memory is released.
+#include <cuda.h>
+#include <cstring>
+#include <mutex>
 #include "common.cuh"
 #include "launchers.h"
+#include "sm100_ptx.cuh"
+
 namespace tuna {
-int launch_gemm_umma(const GemmArgs &, const tuna_config &) { return TUNA_ERR_BAD_CONFIG; }
-size_t gemm_umma_workspace_bytes(int, int, int, const tuna_config &, int) { return 0; }
-int gemm_umma_normalize_config(int, int, int, int, tuna_config *) { return TUNA_ERR_BAD_CONFIG; }
-int gemm_umma_read_status(cudaStream_t) { return TUNA_OK; }
+
+constexpr int kChunkK = 64;                    // K extent of one pipeline stage
+constexpr int kBlockRows = 128;                // rows of one MMA (TMEM lanes)
+constexpr int kWBlockBytes = kBlockRows * kChunkK / 2;  // 4096: packed bytes of one block-stage
+constexpr int kSlotCols = kChunkK / 2;         // 32 TMEM columns hold one block-stage of fp16 A
+constexpr int kUmmaLutBytes = 256 * 32 * 4;
+constexpr int kTmemCols = 512;
+constexpr int kFirstDequantWarp = 6;
+constexpr int kMaxDequantWarps = 16;
+constexpr int kMaxThreads = 32 * (kFirstDequantWarp + kMaxDequantWarps);
+
+struct UmmaParams {
+    const float *code;
+    const float *absmax;
+    __half *o;
+    float *partials;
+    unsigned int *counters;
+    DeviceStatus *status;
+    int m, n, k;
+    int row_blocks;   // J
+    int chunks;       // C = ceil(k / 64)
+    int row_tiles;    // ceil(m / (128 J))
+    int tok_tiles;    // ceil(n / tile_tok)
+    long long units;  // row_tiles * tok_tiles * C
+    int sw, sx, sa, nd;
+    int k_accs;       // accumulators a K chunk's four MMAs are spread over (1, 2 or 4)
+    int dq_groups;
+};
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate)
+{
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_st_x32(uint32_t taddr, const uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_ld_x16(uint32_t taddr, float (&v)[16])
+{
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile stored with the 128-byte swizzle:
+// rows of 64 fp16 (128 bytes), 8-row groups 1024 bytes apart (stride byte offset), version 1,
+// layout type 2 (SWIZZLE_128B).  Advancing K by 16 elements adds 32 bytes to the start address.
+__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr)
+{
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor, kind::f16: D fp32 (bits 4-5 = 1), A and B fp16 (0), both K-major,
+// N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__host__ __device__ constexpr uint32_t make_idesc(int n_tile)
+{
+    return (1u << 4) | ((uint32_t)(n_tile >> 3) << 17) | ((uint32_t)(kBlockRows >> 4) << 24);
+}
+
+// Which weight row a TMEM lane holds.  Lane 32*quarter + l of a 128-row block takes row
+// 8*rg + (l & 7) with rg = 8*(quarter >> 1) + (quarter & 1) + 2*(l >> 3): the four row groups a
+// warp reads at once differ in bits 1-2 of rg, which is what the 128-byte swizzle XORs into
+// the 16-byte chunk index, so the warp's 32-bit reads of the staged bytes are bank-conflict free.
+__device__ __forceinline__ int lane_row_group(int quarter, int l) { return 8 * (quarter >> 1) + (quarter & 1) + 2 * (l >> 3); }
+
+struct UnitCursor {
+    long long u, u_end;
+    int chunk, tile;
+    __device__ void init(const UmmaParams &p, int cta, int ctas)
+    {
+        u = (p.units * cta) / ctas;
+        u_end = (p.units * (cta + 1)) / ctas;
+        tile = (int)(u / p.chunks);
+        chunk = (int)(u - (long long)tile * p.chunks);
+    }
+    __device__ bool valid() const { return u < u_end; }
+    __device__ void next(const UmmaParams &p)
+    {
+        ++u;
+        if (++chunk == p.chunks) { chunk = 0; ++tile; }
+    }
+};
+
+template <int N_TILE>
+__global__ void __launch_bounds__(kMaxThreads, 1)
+gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_q,
+                       const __grid_constant__ CUtensorMap tmap_x)
+{
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ __align__(8) uint64_t bars[96];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+    __shared__ int s_last;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int J = p.row_blocks;
+    const int SW = p.sw, SX = p.sx, SA = p.sa, ND = p.nd;
+    const int ctas = gridDim.x, cta = blockIdx.x;
+
+    uint32_t *lut = reinterpret_cast<uint32_t *>(smem);
+    const uint32_t wring = smem_u32(smem + kUmmaLutBytes);
+    const uint32_t xring = wring + (uint32_t)SW * J * kWBlockBytes;
+    constexpr uint32_t kXStageBytes = N_TILE * kChunkK * 2;
+
+    // barrier ring bases (indices into bars[])
+    const uint32_t bar0 = smem_u32(&bars[0]);
+    const uint32_t w_full = bar0, w_empty = w_full + 8 * SW;
+    const uint32_t x_full = w_empty + 8 * SW, x_empty = x_full + 8 * SX;
+    const uint32_t a_full = x_empty + 8 * SX, a_empty = a_full + 8 * SA;
+    const uint32_t d_full = a_empty + 8 * SA, d_empty = d_full + 8 * ND;
+    const uint32_t epi_bar = d_empty + 8 * ND;  // the 128 epilogue threads' own barrier
+    volatile int *abort_flag = &s_abort;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        s_last = 0;
+        for (int i = 0; i < SW; ++i) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, 4 * J); }
+        for (int i = 0; i < SX; ++i) { mbar_init(x_full + 8 * i, 1); mbar_init(x_empty + 8 * i, 1); }
+        for (int i = 0; i < SA; ++i) { mbar_init(a_full + 8 * i, 4); mbar_init(a_empty + 8 * i, 1); }
+        for (int i = 0; i < ND; ++i) { mbar_init(d_full + 8 * i, 1); mbar_init(d_empty + 8 * i, 4); }
+        mbar_init(epi_bar, 128);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // byte -> half2 table (even column = high nibble in the low half), one copy per bank
+    for (int e = warp; e < 256; e += blockDim.x >> 5) {
+        const __half hi = __float2half_rn(p.code[e >> 4]);
+        const __half lo = __float2half_rn(p.code[e & 15]);
+        lut[e * 32 + lane] = (uint32_t)__half_as_ushort(hi) | ((uint32_t)__half_as_ushort(lo) << 16);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+    const int KA = p.k_accs;
+    const uint32_t d_cols = (uint32_t)J * KA * N_TILE;     // columns of one accumulator buffer
+    const uint32_t a_base = tmem + (uint32_t)ND * d_cols;  // first A-operand slot
+
+    PROF_ROLE_BEGIN();
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            UnitCursor c;
+            c.init(p, cta, ctas);
+            const int n_rg = p.m >> 3;
+            Ring rw, rx;
+            for (; c.valid(); c.next(p), rw.advance(SW), rx.advance(SX)) {
+                const int rt = c.tile / p.tok_tiles, tt = c.tile - rt * p.tok_tiles;
+                const int sw = rw.idx, sx = rx.idx;
+                if (!mbar_wait(w_empty + 8 * sw, rw.phase ^ 1, abort_flag, p.status, 1)) break;
+                int blocks_in = 0;
+                for (int j = 0; j < J; ++j)
+                    if ((rt * J + j) * 16 < n_rg) ++blocks_in;
+                mbar_expect_tx(w_full + 8 * sw, (uint32_t)blocks_in * kWBlockBytes);
+                for (int j = 0; j < blocks_in; ++j) {
+                    const uint32_t dst = wring + (uint32_t)(sw * J + j) * kWBlockBytes;
+                    tma_load_2d(dst, &tmap_q, c.chunk * 256, (rt * J + j) * 16, w_full + 8 * sw);
+                    tma_load_2d(dst + 2048, &tmap_q, c.chunk * 256 + 128, (rt * J + j) * 16, w_full + 8 * sw);
+                }
+                if (!mbar_wait(x_empty + 8 * sx, rx.phase ^ 1, abort_flag, p.status, 2)) break;
+                mbar_expect_tx(x_full + 8 * sx, kXStageBytes);
+                tma_load_2d(xring + (uint32_t)sx * kXStageBytes, &tmap_x, c.chunk * kChunkK, tt * N_TILE, x_full + 8 * sx);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            UnitCursor c;
+            c.init(p, cta, ctas);
+            constexpr uint32_t idesc = make_idesc(N_TILE);
+            Ring rx, ra, rd;
+            bool ok = true;
+            const long long u_first = c.u;
+            for (; ok && c.valid(); c.next(p), rx.advance(SX)) {
+                const bool first = (c.u == u_first) || (c.chunk == 0);
+                const bool last = (c.u + 1 == c.u_end) || (c.chunk + 1 == p.chunks);
+                const int dbuf = rd.idx;
+                if (first) {
+                    if (!mbar_wait(d_empty + 8 * dbuf, rd.phase ^ 1, abort_flag, p.status, 3)) break;
+                    tc_fence_after();
+                }
+                const int sx = rx.idx;
+                if (!mbar_wait(x_full + 8 * sx, rx.phase, abort_flag, p.status, 4)) break;
+                const uint32_t xbase = xring + (uint32_t)sx * kXStageBytes;
+                // Dependent MMAs (same accumulator) are far slower back to back than independent
+                // ones when N is small, so the unit's J x 4 MMAs are issued k-step-major over
+                // J x k_accs accumulators; the epilogue adds the k_accs partial accumulators.
+                int slots[4];
+                for (int j = 0; j < J; ++j, ra.advance(SA)) {
+                    slots[j] = ra.idx;
+                    if (!mbar_wait(a_full + 8 * ra.idx, ra.phase, abort_flag, p.status, 5)) { ok = false; break; }
+                }
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kChunkK / 16; ++kk) {
+                    const int a = kk & (KA - 1);
+                    const uint64_t bdesc = make_b_desc(xbase + kk * 32);
+                    for (int j = 0; j < J; ++j) {
+                        const uint32_t d_t = tmem + (uint32_t)dbuf * d_cols + (uint32_t)(j * KA + a) * N_TILE;
+                        const uint32_t a_t = a_base + (uint32_t)slots[j] * kSlotCols + kk * 8;
+                        tc_mma_ts(d_t, a_t, bdesc, idesc, (first && kk < KA) ? 0u : 1u);
+                    }
+                }
+                for (int j = 0; j < J; ++j) tc_commit(a_empty + 8 * slots[j]);
+                if (!ok) break;
+                tc_commit(x_empty + 8 * sx);
+                if (last) {
+                    tc_commit(d_full + 8 * dbuf);
+                    rd.advance(ND);
+                }
+            }
+        }
+    } else if (warp < kFirstDequantWarp) {
+        // ------------------------------------------------------------------ epilogue
+        const int quarter = warp & 3;
+        const int et = (warp - 2) * 32 + lane;  // 0..127 among the epilogue threads
+        const int row_in_block = 8 * lane_row_group(quarter, lane) + (lane & 7);
+        const int tmem_lane = 32 * quarter + lane;
+        UnitCursor c;
+        c.init(p, cta, ctas);
+        Ring rd;
+        uint32_t epi_phase = 0;
+        // bounded rendezvous of the 128 epilogue threads (a bar.sync could not give up)
+        auto epi_sync = [&]() -> bool {
+            mbar_arrive(epi_bar);
+            const bool r = mbar_wait(epi_bar, epi_phase & 1, abort_flag, p.status, 9);
+            ++epi_phase;
+            return r;
+        };
+        while (c.valid()) {
+            // the segment: units of one tile inside this CTA's range
+            const int tile = c.tile, c0 = c.chunk;
+            const long long left = c.u_end - c.u;
+            const int c1 = (int)((long long)(p.chunks - c0) <= left ? p.chunks : c0 + left);
+            const int rt = tile / p.tok_tiles, tt = tile - rt * p.tok_tiles;
+            const bool full = (c0 == 0 && c1 == p.chunks);
+            const int dbuf = rd.idx;
+            if (!mbar_wait(d_full + 8 * dbuf, rd.phase, abort_flag, p.status, 6)) break;
+            tc_fence_after();
+            const size_t slot_floats = (size_t)J * kBlockRows * N_TILE;
+            float *my_partial = p.partials + (size_t)(2 * cta + (c0 == 0 ? 1 : 0)) * slot_floats;
+            for (int j = 0; j < J; ++j) {
+                const int row = (rt * J + j) * kBlockRows + row_in_block;
+                const float sc = (row < p.m) ? p.absmax[row] : 0.f;
+#pragma unroll 1
+                for (int piece = 0; piece < N_TILE / 16; ++piece) {
+                    float v[16];
+                    const uint32_t t0 = tmem + ((uint32_t)(32 * quarter) << 16) + (uint32_t)dbuf * d_cols + (uint32_t)(j * KA) * N_TILE + piece * 16;
+                    tc_ld_x16(t0, v);
+                    for (int a = 1; a < KA; ++a) {
+                        float v2[16];
+                        tc_ld_x16(t0 + (uint32_t)a * N_TILE, v2);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] += v2[i];
+                    }
+                    if (full) {
+                        if (row < p.m) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const int tok = tt * N_TILE + piece * 16 + i;
+                                if (tok < p.n) p.o[(size_t)tok * p.m + row] = __float2half_rn(v[i] * sc);
+                            }
+                        }
+                    } else {
+                        float4 *dst = reinterpret_cast<float4 *>(my_partial + ((size_t)j * kBlockRows + tmem_lane) * N_TILE + piece * 16);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(d_empty + 8 * dbuf);
+            if (!full) {
+                // last arriver at the tile's counter adds every partial in unit order
+                __threadfence();
+                if (!epi_sync()) break;
+                const int cta_first = cta_of_unit((long long)tile * p.chunks, p.units, ctas);
+                const int cta_last = cta_of_unit((long long)(tile + 1) * p.chunks - 1, p.units, ctas);
+                const int nseg = cta_last - cta_first + 1;
+                if (et == 0) {
+                    const unsigned int old = atomicAdd(&p.counters[tile], 1u);
+                    const int is_last = (old == (unsigned)nseg - 1);
+                    if (is_last) p.counters[tile] = 0;
+                    s_last = is_last;
+                }
+                if (!epi_sync()) break;
+                const int is_last = s_last;
+                if (!epi_sync()) break;  // s_last may be rewritten by the next segment
+                if (is_last) {
+                    __threadfence();
+                    for (int j = 0; j < J; ++j) {
+                        const int row = (rt * J + j) * kBlockRows + row_in_block;
+                        if (row >= p.m) continue;
+                        const float sc = p.absmax[row];
+#pragma unroll 1
+                        for (int piece = 0; piece < N_TILE / 16; ++piece) {
+                            float acc[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+                            for (int s = 0; s < nseg; ++s) {
+                                const float4 *src = reinterpret_cast<const float4 *>(
+                                    p.partials + (size_t)(2 * (cta_first + s) + (s == 0 ? 1 : 0)) * slot_floats +
+                                    ((size_t)j * kBlockRows + tmem_lane) * N_TILE + piece * 16);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const float4 t4 = __ldcg(src + i);
+                                    acc[4 * i] += t4.x; acc[4 * i + 1] += t4.y; acc[4 * i + 2] += t4.z; acc[4 * i + 3] += t4.w;
+                                }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const int tok = tt * N_TILE + piece * 16 + i;
+                                if (tok < p.n) p.o[(size_t)tok * p.m + row] = __float2half_rn(acc[i] * sc);
+                            }
+                        }
+                    }
+                }
+            }
+            // advance the cursor past this segment
+            const int n_adv = c1 - c0;
+            c.u += n_adv;
+            c.chunk += n_adv;
+            if (c.chunk == p.chunks) { c.chunk = 0; ++c.tile; }
+            rd.advance(ND);
+        }
+    } else {
+        // ------------------------------------------------------------------ dequant
+        const int quarter = warp & 3;
+        const int group = (warp - kFirstDequantWarp) >> 2;
+        const int G = p.dq_groups;
+        const int rg = lane_row_group(quarter, lane), r = lane & 7;
+        // byte offsets of this lane's four 32-bit words inside one 2-KB swizzled box
+        uint32_t off[4];
+#pragma unroll
+        for (int kt = 0; kt < 4; ++kt)
+            off[kt] = (uint32_t)rg * 128 + ((uint32_t)((2 * kt + (r >> 2)) ^ (rg & 7)) << 4) + (uint32_t)(r & 3) * 4;
+        const uint32_t *lut_lane = lut + lane;
+        UnitCursor c;
+        c.init(p, cta, ctas);
+        Ring rw, ra;
+        int turn = 0;  // task index modulo the number of dequant groups
+        bool ok = true;
+        for (; ok && c.valid(); c.next(p), rw.advance(SW)) {
+            const int sw = rw.idx;
+            bool waited = false;
+            for (int j = 0; j < J; ++j, ra.advance(SA), turn = (turn + 1 == G) ? 0 : turn + 1) {
+                if (turn != group) continue;
+                if (!waited) {
+                    if (!mbar_wait(w_full + 8 * sw, rw.phase, abort_flag, p.status, 7)) { ok = false; break; }
+                    waited = true;
+                }
+                const int slot = ra.idx;
+                const uint32_t wb = wring + (uint32_t)(sw * J + j) * kWBlockBytes;
+                uint32_t w[8];
+#pragma unroll
+                for (int kt = 0; kt < 8; ++kt)
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[kt]) : "r"(wb + (kt >> 2) * 2048 + off[kt & 3]));
+                uint32_t v[32];
+#pragma unroll
+                for (int kt = 0; kt < 8; ++kt)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) v[kt * 4 + b] = lut_lane[((w[kt] >> (8 * b)) & 0xffu) * 32];
+                if (!mbar_wait(a_empty + 8 * slot, ra.phase ^ 1, abort_flag, p.status, 8)) { ok = false; break; }
+                tc_fence_after();
+                tc_st_x32(a_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)slot * kSlotCols, v);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(a_full + 8 * slot);
+                    mbar_arrive(w_empty + 8 * sw);
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------ common exit
+    PROF_ROLE_END(warp < kFirstDequantWarp ? warp : kFirstDequantWarp);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+static int pick_tile_tok(int n)
+{
+    for (int t : {16, 32, 64, 128})
+        if (n <= t) return t;
+    return 256;
+}
+
+// Two accumulator buffers (epilogue of one segment overlaps the MMAs of the next) when they
+// leave at least four A-operand slots in the 512 TMEM columns.
+static int umma_num_dbuf(const tuna_config &c)
+{
+    const int dcols = c.row_blocks * c.k_accs * c.tile_tok;
+    return (2 * dcols + 4 * kSlotCols <= kTmemCols) ? 2 : 1;
+}
+
+static size_t umma_smem_bytes(const tuna_config &c)
+{
+    const size_t b = (size_t)kUmmaLutBytes + (size_t)c.stages_w * c.row_blocks * kWBlockBytes +
+                     (size_t)c.stages_x * c.tile_tok * kChunkK * 2;
+    const size_t floor_1cta = 120 * 1024;  // more than half an SM: never two CTAs (two 512-column TMEM requests) per SM
+    return b > floor_1cta ? b : floor_1cta;
+}
+
+int gemm_umma_normalize_config(int m, int n, int k, int sm_count, tuna_config *c)
+{
+    (void)m; (void)k;
+    if (c->tile_tok == 0) c->tile_tok = pick_tile_tok(n);
+    const int t = c->tile_tok;
+    if (t != 16 && t != 32 && t != 64 && t != 128 && t != 256) return TUNA_ERR_BAD_CONFIG;
+    if (c->row_blocks == 0) c->row_blocks = (t <= 32) ? 4 : (t <= 64 ? 2 : 1);
+    if (c->row_blocks != 1 && c->row_blocks != 2 && c->row_blocks != 4) return TUNA_ERR_BAD_CONFIG;
+    if (c->dequant_warps == 0) c->dequant_warps = 16;
+    if (c->dequant_warps % 4 || c->dequant_warps < 4 || c->dequant_warps > kMaxDequantWarps) return TUNA_ERR_BAD_CONFIG;
+    if (c->k_accs == 0) c->k_accs = (t <= 32) ? 4 : (t <= 64 ? 2 : 1);
+    if (c->k_accs != 1 && c->k_accs != 2 && c->k_accs != 4) return TUNA_ERR_BAD_CONFIG;
+    const int dcols = c->row_blocks * c->k_accs * t;
+    if (dcols > 256) return TUNA_ERR_BAD_CONFIG;
+    const int nd = umma_num_dbuf(*c);
+    const int max_sa = (kTmemCols - nd * dcols) / kSlotCols;
+    if (c->stages_a == 0) c->stages_a = max_sa < 8 ? max_sa : 8;
+    if (c->stages_a < 2 || c->stages_a > max_sa) return TUNA_ERR_BAD_CONFIG;
+    if (c->stages_w == 0) c->stages_w = (c->row_blocks == 4) ? 4 : (c->row_blocks == 2 ? 6 : 8);
+    if (c->stages_x == 0) c->stages_x = (t >= 128) ? 4 : 6;
+    if (c->stages_w < 2 || c->stages_x < 2 || c->stages_w > 16 || c->stages_x > 16) return TUNA_ERR_BAD_CONFIG;
+    if (2 * c->stages_w + 2 * c->stages_x + 2 * c->stages_a + 5 > 96) return TUNA_ERR_BAD_CONFIG;
+    if (umma_smem_bytes(*c) > 225 * 1024) return TUNA_ERR_BAD_CONFIG;
+    if (c->ctas < 0) return TUNA_ERR_BAD_CONFIG;
+    if (c->ctas == 0 || c->ctas > sm_count) c->ctas = sm_count;
+    return TUNA_OK;
+}
+
+static long long umma_units(int m, int n, int k, const tuna_config &c)
+{
+    const long long rt = div_up(m, kBlockRows * c.row_blocks), tt = div_up(n, c.tile_tok), ch = div_up(k, kChunkK);
+    return rt * tt * ch;
+}
+
+size_t gemm_umma_workspace_bytes(int m, int n, int k, const tuna_config &c, int sm_count)
+{
+    (void)sm_count;
+    const long long tiles = (long long)div_up(m, kBlockRows * c.row_blocks) * div_up(n, c.tile_tok);
+    const size_t counters = ((size_t)tiles * 4 + 255) / 256 * 256;
+    const size_t slot = (size_t)c.row_blocks * kBlockRows * c.tile_tok * 4;
+    return counters + 2 * (size_t)c.ctas * slot;
+}
+
+#ifdef TUNA_PROFILE
+extern "C" void tunadbg_prof(long long *out, int reset)
+{
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 32);
+    if (reset) {
+        long long z[32] = {0};
+        cudaMemcpyToSymbol(g_prof, z, sizeof(z));
+    }
+}
+#endif
+
+template <int N_TILE>
+static int launch_umma(const UmmaParams &p, const CUtensorMap &mq, const CUtensorMap &mx, int ctas, int threads,
+                       size_t smem, cudaStream_t stream)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(gemm_w4a16_umma_kernel<N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 225 * 1024) != cudaSuccess)
+            return TUNA_ERR_NO_DEVICE;
+        attr_set = true;
+    }
+    gemm_w4a16_umma_kernel<N_TILE><<<ctas, threads, smem, stream>>>(p, mq, mx);
+    return cudaGetLastError() == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
+}
+
+int launch_gemm_umma(const GemmArgs &a, const tuna_config &c)
+{
+    UmmaParams p;
+    p.code = a.code; p.absmax = a.absmax; p.o = (__half *)a.o;
+    p.m = a.m; p.n = a.n; p.k = a.k;
+    p.row_blocks = c.row_blocks;
+    p.chunks = div_up(a.k, kChunkK);
+    p.row_tiles = div_up(a.m, kBlockRows * c.row_blocks);
+    p.tok_tiles = div_up(a.n, c.tile_tok);
+    p.units = umma_units(a.m, a.n, a.k, c);
+    p.sw = c.stages_w; p.sx = c.stages_x; p.sa = c.stages_a;
+    p.nd = umma_num_dbuf(c);
+    p.k_accs = c.k_accs;
+    p.dq_groups = c.dequant_warps / 4;
+    p.status = device_status_word();
+    if (!p.status) return TUNA_ERR_NO_DEVICE;
+    const long long tiles = (long long)p.row_tiles * p.tok_tiles;
+    const size_t counters = ((size_t)tiles * 4 + 255) / 256 * 256;
+    int ctas = c.ctas;
+    if ((long long)ctas > p.units) ctas = (int)p.units;
+    tuna_config cc = c;
+    cc.ctas = c.ctas;
+    if (a.workspace == nullptr || a.workspace_bytes < gemm_umma_workspace_bytes(a.m, a.n, a.k, cc, a.sm_count))
+        return TUNA_ERR_WORKSPACE;
+    p.counters = (unsigned int *)a.workspace;
+    p.partials = (float *)((uint8_t *)a.workspace + counters);
+
+    CUtensorMap mq, mx;
+    // packed weights as [m/8 row groups][4k bytes]; box = 16 row groups x 128 bytes (32 columns)
+    if (!make_tensor_map_2d(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.q, (uint64_t)a.k * 4, (uint64_t)a.m / 8,
+                            (uint64_t)a.k * 4, 128, 16, CU_TENSOR_MAP_SWIZZLE_128B))
+        return TUNA_ERR_NO_DEVICE;
+    // activations as [n][k] fp16; box = tile_tok tokens x 64 columns
+    if (!make_tensor_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.x, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.k * 2,
+                            kChunkK, (uint32_t)c.tile_tok, CU_TENSOR_MAP_SWIZZLE_128B))
+        return TUNA_ERR_NO_DEVICE;
+
+    const int threads = 32 * (kFirstDequantWarp + c.dequant_warps);
+    const size_t smem = umma_smem_bytes(c);
+    switch (c.tile_tok) {
+        case 16: return launch_umma<16>(p, mq, mx, ctas, threads, smem, a.stream);
+        case 32: return launch_umma<32>(p, mq, mx, ctas, threads, smem, a.stream);
+        case 64: return launch_umma<64>(p, mq, mx, ctas, threads, smem, a.stream);
+        case 128: return launch_umma<128>(p, mq, mx, ctas, threads, smem, a.stream);
+        case 256: return launch_umma<256>(p, mq, mx, ctas, threads, smem, a.stream);
+        default: return TUNA_ERR_BAD_CONFIG;
+    }
+}
+
+}  // namespace tuna

@@ -1,0 +1,71 @@
+// Host-side helpers shared by the pipeline kernels' launchers: the per-device status word that
+// bounded waits report into, and TMA tensor-map construction through the driver entry point
+// (resolved at run time, so the library does not link against libcuda).
+#include <mutex>
+#include "common.cuh"
+#include "launchers.h"
+
+namespace tuna {
+
+DeviceStatus *device_status_word()
+{
+    static DeviceStatus *ptrs[64] = {nullptr};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[dev]) {
+        DeviceStatus *p = nullptr;
+        if (cudaMalloc(&p, sizeof(DeviceStatus)) != cudaSuccess) return nullptr;
+        cudaMemset(p, 0, sizeof(DeviceStatus));
+        ptrs[dev] = p;
+    }
+    return ptrs[dev];
+}
+
+int read_device_status(cudaStream_t stream)
+{
+    DeviceStatus *d = device_status_word();
+    if (!d) return TUNA_ERR_NO_DEVICE;
+    DeviceStatus h;
+    if (cudaMemcpyAsync(&h, d, sizeof(h), cudaMemcpyDeviceToHost, stream) != cudaSuccess) return TUNA_ERR_LAUNCH;
+    if (cudaStreamSynchronize(stream) != cudaSuccess) return TUNA_ERR_LAUNCH;
+    if (h.code != 0) {
+        cudaMemsetAsync(d, 0, sizeof(DeviceStatus), stream);
+        return TUNA_ERR_DEVICE_TIMEOUT;
+    }
+    return TUNA_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    });
+    return fn;
+}
+
+bool make_tensor_map_2d(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t inner, uint64_t outer,
+                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace tuna

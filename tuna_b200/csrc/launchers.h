@@ -1,5 +1,6 @@
 // Internal launcher interface between the C ABI (tuna_api.cu) and the kernels.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -20,6 +21,13 @@ struct GemmArgs {
     int sm_count;
 };
 
+struct DeviceStatus;
+// One zero-initialised status word per device; bounded in-kernel waits report into it.
+DeviceStatus *device_status_word();
+int read_device_status(cudaStream_t stream);
+bool make_tensor_map_2d(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t inner, uint64_t outer,
+                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle);
+
 cudaError_t launch_dequant(const void *q, const void *absmax, const void *code, void *o, int m,
                            int k, int sm_count, cudaStream_t stream);
 
@@ -32,6 +40,5 @@ int gemm_stream_normalize_config(int m, int n, int k, int sm_count, tuna_config 
 int launch_gemm_umma(const GemmArgs &a, const tuna_config &cfg);
 size_t gemm_umma_workspace_bytes(int m, int n, int k, const tuna_config &cfg, int sm_count);
 int gemm_umma_normalize_config(int m, int n, int k, int sm_count, tuna_config *cfg);
-int gemm_umma_read_status(cudaStream_t stream);
 
 }  // namespace tuna

@@ -1,0 +1,103 @@
+// mbarrier / TMA wrappers and the bounded-wait protocol shared by the sm_100a pipeline kernels.
+#pragma once
+#include <cuda.h>
+#include "common.cuh"
+
+namespace tuna {
+
+constexpr long long kWaitCycles = 4000000000ll;  // ~2 s at 1.9 GHz
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false when the time limit ran out or another role raised the abort
+// flag; the caller unwinds.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                            DeviceStatus *status, int where)
+{
+    const long long t0 = clock64();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitCycles) {
+            *abort_flag = 1;
+            if (atomicCAS(&status->code, 0, where) == 0) status->detail = (int)blockIdx.x;
+            return false;
+        }
+    }
+}
+#ifdef TUNA_PROFILE
+// Debug build only: cycles CTA 0 spends in each wait site ([where]) and in each role ([16 + role]).
+__device__ long long g_prof[32];
+#define PROF_ROLE_BEGIN() const long long _role_t0 = clock64()
+#define PROF_ROLE_END(role)                                                            \
+    do {                                                                               \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_prof[16 + (role)] = clock64() - _role_t0; \
+    } while (0)
+#else
+#define PROF_ROLE_BEGIN()
+#define PROF_ROLE_END(role)
+#endif
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          DeviceStatus *status, int where)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+#ifdef TUNA_PROFILE
+    const long long t0 = clock64();
+    const bool r = mbar_wait_slow(bar, parity, abort_flag, status, where);
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_prof[where] += clock64() - t0;
+    return r;
+#else
+    return mbar_wait_slow(bar, parity, abort_flag, status, where);
+#endif
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+
+
+// Position in a ring of n mbarrier-guarded buffers: slot index and the parity of its current use.
+struct Ring {
+    int idx;
+    uint32_t phase;
+    __device__ Ring() : idx(0), phase(0) {}
+    __device__ void advance(int n)
+    {
+        if (++idx == n) { idx = 0; phase ^= 1u; }
+    }
+};
+
+// The CTA i whose contiguous range [floor(i*U/G), floor((i+1)*U/G)) holds unit u.
+__device__ __forceinline__ int cta_of_unit(long long u, long long units, int ctas)
+{
+    return (int)(((u + 1) * ctas + units - 1) / units) - 1;
+}
+
+}  // namespace tuna

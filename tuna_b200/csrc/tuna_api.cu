@@ -143,7 +143,7 @@ extern "C" int tuna_dequant(const void *q, const void *absmax, const void *code,
     return e == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
 }
 
-extern "C" int tuna_check_device_status(void *stream) { return gemm_umma_read_status((cudaStream_t)stream); }
+extern "C" int tuna_check_device_status(void *stream) { return read_device_status((cudaStream_t)stream); }
 
 extern "C" const char *tuna_status_string(int s)
 {

@@ -45,7 +45,7 @@ typedef enum tuna_status {
 /* Which kernel family a launch uses.  AUTO lets the shape table decide. */
 typedef enum tuna_path {
     TUNA_PATH_AUTO = 0,
-    TUNA_PATH_STREAM = 1, /* TMA-fed mma.sync weight-streaming kernel, small token counts */
+    TUNA_PATH_STREAM = 1, /* register-streaming mma.sync kernel, small token counts       */
     TUNA_PATH_UMMA = 2    /* tcgen05/TMEM kernel: TMA-staged, dequant into TMEM       */
 } tuna_path;
 
@@ -58,9 +58,9 @@ typedef struct tuna_config {
     int32_t rows_per_warp; /* stream: 32-row blocks per warp (1|2)                    */
     int32_t warps_m;       /* stream: consumer warps along output rows (power of 2)   */
     int32_t warps_k;       /* stream: consumer warps along K (power of 2, m*k <= 16)  */
-    int32_t k_steps;       /* stream: 32-column steps per warp per stage (1|2)        */
+    int32_t k_steps;       /* stream: 32-column steps per warp per unit (8|16|32|64)  */
     int32_t ctas;          /* persistent CTAs (0 = one per SM)                        */
-    int32_t stages_w;      /* packed-weight ring depth (upper bound for stream)       */
+    int32_t stages_w;      /* umma: packed-weight ring depth (64-column stages)       */
     int32_t stages_x;      /* umma: activation ring depth                             */
     int32_t dequant_warps; /* umma: warps converting codes into TMEM (mult of 4)      */
     int32_t row_blocks;    /* umma: 128-row blocks per CTA tile (1|2|4)               */

@@ -41,8 +41,8 @@ def test_render_rejects_bad_entries():
 
 def test_render_field_order():
     text = make_configs.render({"4096_16_4096": {"path": "stream", "tile_tok": 16, "rows_per_warp": 2,
-                                                 "warps_m": 4, "warps_k": 4, "k_steps": 2, "us": 4.2}})
-    assert "{4096, 16, 4096, {1, 16, 2, 4, 4, 2, 0, 0, 0, 0, 0, 0, 0, {0, 0, 0}}}," in text
+                                                 "warps_m": 4, "warps_k": 4, "k_steps": 8, "us": 4.2}})
+    assert "{4096, 16, 4096, {1, 16, 2, 4, 4, 8, 0, 0, 0, 0, 0, 0, 0, {0, 0, 0}}}," in text
 
 
 @pytest.mark.parametrize("n", [1, 8, 16])
@@ -53,7 +53,7 @@ def test_lookup_always_yields_a_runnable_config(tuna_lib, m, k, n):
     assert cfg.path in (_lib.PATH_STREAM, _lib.PATH_UMMA)
     if cfg.path == _lib.PATH_STREAM:
         assert cfg.tile_tok in (8, 16, 32) and cfg.rows_per_warp in (1, 2)
-        assert 1 <= cfg.warps_m * cfg.warps_k <= 16 and cfg.k_steps in (1, 2)
+        assert 1 <= cfg.warps_m * cfg.warps_k <= 16 and cfg.k_steps in (4, 8, 16, 32, 64)
     ws = tuna_lib.tuna_matmul_workspace_bytes(m, n, k)
     assert ws < (1 << 31)
 

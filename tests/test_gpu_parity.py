@@ -134,9 +134,9 @@ def test_matmul_is_deterministic_and_needs_no_zero_fill(m, k, n):
 STREAM_CONFIGS = [
     dict(rows_per_warp=r, warps_m=wm, warps_k=wk, k_steps=ks, tile_tok=tt, ctas=ctas)
     for (r, wm, wk, ks, tt, ctas) in [
-        (1, 1, 1, 1, 16, 0), (1, 16, 1, 2, 16, 0), (1, 1, 16, 1, 16, 0), (2, 4, 4, 2, 16, 0), (2, 16, 1, 1, 16, 0),
-        (2, 2, 8, 2, 16, 3), (2, 8, 2, 1, 16, 7), (1, 4, 4, 2, 8, 0), (2, 16, 1, 2, 8, 5), (2, 2, 2, 1, 8, 148),
-        (1, 8, 2, 2, 32, 0), (1, 2, 4, 1, 32, 11),
+        (1, 1, 1, 8, 16, 0), (1, 16, 1, 8, 16, 0), (1, 4, 4, 8, 16, 0), (2, 4, 4, 4, 16, 0), (2, 16, 1, 16, 16, 0),
+        (2, 2, 8, 4, 16, 3), (2, 8, 2, 4, 16, 7), (1, 4, 4, 8, 8, 0), (2, 16, 1, 4, 8, 5), (2, 2, 2, 8, 8, 148),
+        (1, 16, 1, 8, 32, 0), (1, 4, 2, 8, 32, 11),
     ]
 ]
 

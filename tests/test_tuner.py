@@ -1,0 +1,35 @@
+"""Host logic of the tuner: genome handling and configuration validity, no GPU needed."""
+
+import random
+
+from tuna_b200 import _lib, tuner
+
+
+def test_genomes_stay_inside_the_search_space():
+    rng = random.Random(0)
+    for path in ("stream", "umma"):
+        space = tuner.space_for(path)
+        g = tuner.random_genome(rng, path)
+        for _ in range(50):
+            g = tuner.mutate(rng, tuner.crossover(rng, g, tuner.random_genome(rng, path)), path)
+            assert set(g) == set(space)
+            assert all(g[k] in space[k] for k in g)
+
+
+def test_validity_filter_matches_the_launcher(tuna_lib):
+    ok = tuner.to_config("stream", 16, dict(rows_per_warp=1, warps_m=16, warps_k=1, k_steps=8))
+    assert tuner.is_valid(tuna_lib, 4096, 16, 4096, ok)
+    too_many_warps = tuner.to_config("stream", 16, dict(rows_per_warp=1, warps_m=16, warps_k=2, k_steps=8))
+    assert not tuner.is_valid(tuna_lib, 4096, 16, 4096, too_many_warps)
+    bad_steps = tuner.to_config("stream", 16, dict(rows_per_warp=1, warps_m=16, warps_k=1, k_steps=4))
+    assert not tuner.is_valid(tuna_lib, 4096, 16, 4096, bad_steps)
+    umma = tuner.to_config("umma", 256, dict(row_blocks=1, stages_w=4, stages_x=4, stages_a=4, dequant_warps=16, k_accs=1))
+    assert tuner.is_valid(tuna_lib, 4096, 2048, 4096, umma)
+    umma_bad = tuner.to_config("umma", 256, dict(row_blocks=2, stages_w=4, stages_x=4, stages_a=4, dequant_warps=16, k_accs=1))
+    assert not tuner.is_valid(tuna_lib, 4096, 2048, 4096, umma_bad)
+
+
+def test_config_fields_round_trip():
+    cfg = tuner.to_config("umma", 64, dict(row_blocks=2, stages_w=6, stages_x=4, stages_a=8, dequant_warps=8, k_accs=2))
+    d = cfg.as_dict()
+    assert d["path"] == _lib.PATH_UMMA and d["tile_tok"] == 64 and d["row_blocks"] == 2 and d["k_accs"] == 2

@@ -233,13 +233,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
                 a[P][4] = lut_lookup(wa, lane_key, 0x7624); a[P][5] = lut_lookup(wb, lane_key, 0x7624);
                 a[P][6] = lut_lookup(wa, lane_key, 0x7634); a[P][7] = lut_lookup(wb, lane_key, 0x7634);
             }
+            // k-half-major order: the two MMAs into one accumulator are never back to back, so the
+            // accumulate dependency is hidden behind the other accumulators' MMAs
 #pragma unroll
             for (int P = 0; P < 2; ++P)
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    mma_m16n8k16(acc[rr][P][nt], a[P][0], a[P][1], a[P][2], a[P][3], xv[nt].x, xv[nt].y);
-                    mma_m16n8k16(acc[rr][P][nt], a[P][4], a[P][5], a[P][6], a[P][7], xv[nt].z, xv[nt].w);
-                }
+                for (int nt = 0; nt < NT; ++nt) mma_m16n8k16(acc[rr][P][nt], a[P][0], a[P][1], a[P][2], a[P][3], xv[nt].x, xv[nt].y);
+#pragma unroll
+            for (int P = 0; P < 2; ++P)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma_m16n8k16(acc[rr][P][nt], a[P][4], a[P][5], a[P][6], a[P][7], xv[nt].z, xv[nt].w);
         }
     };
 

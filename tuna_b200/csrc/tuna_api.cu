@@ -57,7 +57,7 @@ static int resolve_config(int m, int n, int k, int sm_count, const tuna_config *
         for (int i = 0; i < kTableSize; ++i)
             if (kTable[i].m == m && kTable[i].k == k && kTable[i].n_bucket == b) { c = kTable[i].cfg; break; }
     }
-    if (c.path == TUNA_PATH_AUTO) c.path = (n <= 16) ? TUNA_PATH_STREAM : TUNA_PATH_UMMA;
+    if (c.path == TUNA_PATH_AUTO) c.path = (n <= 32) ? TUNA_PATH_STREAM : TUNA_PATH_UMMA;
     int st;
     if (c.path == TUNA_PATH_STREAM) st = gemm_stream_normalize_config(m, n, k, sm_count, &c);
     else if (c.path == TUNA_PATH_UMMA) st = gemm_umma_normalize_config(m, n, k, sm_count, &c);

@@ -45,6 +45,7 @@
 // The only waits are the rendezvous of the 16 warps at the end of a tile segment; they are
 // bounded (sm100_ptx.cuh): a wait that runs out records where and everybody unwinds.
 #include <cstring>
+#include <mutex>
 #include "common.cuh"
 #include "launchers.h"
 #include "sm100_ptx.cuh"
@@ -493,12 +494,14 @@ size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &c)
 template <int R, int NT>
 static int launch_one(const StreamParams &p, int ctas, size_t smem, cudaStream_t stream)
 {
-    static bool attr_set = false;  // one-time opt-in to large dynamic shared memory
-    if (!attr_set) {
+    static bool attr_set[64] = {false};  // one-time, per device, opt-in to large dynamic shared memory
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TUNA_ERR_NO_DEVICE;
+    if (!attr_set[dev]) {
         if (cudaFuncSetAttribute(gemm_stream_kernel<R, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kStreamSmemLimit) != cudaSuccess)
             return TUNA_ERR_NO_DEVICE;
-        attr_set = true;
+        attr_set[dev] = true;
     }
     gemm_stream_kernel<R, NT><<<ctas, kStreamThreads, smem, stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
@@ -540,3 +543,4 @@ int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)
 }
 
 }  // namespace tuna
+

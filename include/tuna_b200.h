@@ -116,6 +116,30 @@ int tuna_dequant(const void *q, const void *absmax, const void *code, void *o,
  * TUNA_ERR_DEVICE_TIMEOUT if a bounded mbarrier wait gave up. */
 int tuna_check_device_status(void *stream);
 
+/*
+ * The GEMM for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  Some hosts of this library run inside a region where cudaMalloc is off limits: an
+ * inference server that hands all device memory to its own pool at start-up, or code that runs
+ * between the nodes of a latency-critical serving loop where an allocation would synchronise the
+ * device.  For them this entry point takes no workspace: the scratch of the small-token-count
+ * kernel (tile counters and split-K partial tiles) and its status word are file-scope device
+ * arrays of the library, TUNA_NOALLOC_SCRATCH_BYTES in total, which every GPU that loads the
+ * library keeps until the process exits.  It never calls cudaMalloc, cudaFree or an allocating
+ * library routine.
+ *  - Same arguments, layouts and result as tuna_matmul (small-token-count kernel, any n; more than
+ *    32 tokens run as several passes).  A shape whose scratch would exceed the array returns
+ *    TUNA_ERR_TOO_LARGE; with one CTA per SM on a 148-SM part the partial tiles need at most
+ *    19.4 MB, so in practice only the tile counters of matrices beyond ~10^8 rows do not fit.
+ *  - The first call on a device looks up the arrays' device addresses (cudaGetSymbolAddress) and
+ *    opts the kernel into large shared memory; make that first call outside any stream capture.
+ *  - All calls share the one array per device and it keeps the previous call's contents (the part
+ *    that must start at zero is cleared on the stream by every call): calls that overlap on the
+ *    same GPU, on different streams, race.  Use tuna_matmul with separate workspaces for that.
+ */
+#define TUNA_NOALLOC_SCRATCH_BYTES (20u << 20)
+int tuna_matmul_noalloc(const void *q, const void *x, const void *code, const void *absmax, void *o,
+                        int m, int n, int k, void *stream);
+
 const char *tuna_status_string(int status);
 
 /* Library / table identification: ABI version and number of table entries. */

@@ -544,3 +544,93 @@ int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)
 
 }  // namespace tuna
 
+// ------------------------------------------------------------------ entry point that allocates nothing
+//
+// Scratch of the streaming kernel (tile counters + split-K partial tiles) and its status word live
+// in file-scope device arrays, so that a caller that must not allocate device memory while it runs
+// can still use the GEMM.  In host code the array names are only handles: the device addresses come
+// from cudaGetSymbolAddress, looked up once per device with that device current.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[TUNA_NOALLOC_SCRATCH_BYTES];
+static __device__ __align__(256) tuna::DeviceStatus g_noalloc_status;
+
+namespace {
+struct NoAllocDevice {
+    bool ready = false;
+    void *scratch = nullptr;
+    tuna::DeviceStatus *status = nullptr;
+};
+NoAllocDevice g_noalloc_devices[64];
+std::mutex g_noalloc_mutex;
+}  // namespace
+
+extern "C" int tuna_matmul_noalloc(const void *q, const void *x, const void *code, const void *absmax, void *o,
+                                   int m, int n, int k, void *stream)
+{
+    using namespace tuna;
+    if (!q || !x || !code || !absmax || !o) return TUNA_ERR_NULL_POINTER;
+    if (m <= 0 || k <= 0 || n <= 0 || (m % 8) || (k % 8)) return TUNA_ERR_BAD_SHAPE;
+    auto misaligned = [](const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) != 0; };
+    if (misaligned(q, 16) || misaligned(x, 16) || misaligned(o, 16) || misaligned(absmax, 4) || misaligned(code, 4))
+        return TUNA_ERR_MISALIGNED;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TUNA_ERR_NO_DEVICE;
+    NoAllocDevice &d = g_noalloc_devices[dev];
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!d.ready) {  // first call on this device: resolve the device addresses of the two arrays
+            void *p = nullptr, *s = nullptr;
+            if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess) return TUNA_ERR_NO_DEVICE;
+            if (cudaGetSymbolAddress(&s, g_noalloc_status) != cudaSuccess) return TUNA_ERR_NO_DEVICE;
+            d.scratch = p;
+            d.status = (DeviceStatus *)s;
+            d.ready = true;
+        }
+    }
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return TUNA_ERR_NO_DEVICE;
+    tuna_config c;
+    std::memset(&c, 0, sizeof(c));
+    c.path = TUNA_PATH_STREAM;
+    int st = tuna_lookup_config(m, n, k, &c);  // the table's choice when it is a streaming one
+    if (st != TUNA_OK || c.path != TUNA_PATH_STREAM) {
+        std::memset(&c, 0, sizeof(c));
+        c.path = TUNA_PATH_STREAM;
+        st = gemm_stream_normalize_config(m, n, k, sms, &c);
+        if (st != TUNA_OK) return st;
+    }
+    const size_t need = gemm_stream_workspace_bytes(m, n, k, c);
+    if (need > (size_t)TUNA_NOALLOC_SCRATCH_BYTES) return TUNA_ERR_TOO_LARGE;
+    StreamParams geo;
+    stream_geometry(m, k, c, c.tile_tok / 8, &geo);
+    // the counters must start at zero; the array keeps whatever the last call (or an aborted one) left
+    const size_t counters = ((size_t)geo.row_tiles * 4 + 255) / 256 * 256;
+    if (cudaMemsetAsync(d.scratch, 0, counters, (cudaStream_t)stream) != cudaSuccess) return TUNA_ERR_LAUNCH;
+    // same parameter block and launch as launch_gemm_stream, with the static arrays in place of a
+    // caller workspace and of the allocated status word
+    const int nt = c.tile_tok / 8;
+    StreamParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.q = (const uint8_t *)q; p.x = (const __half *)x; p.code = (const float *)code; p.absmax = (const float *)absmax;
+    p.o = (__half *)o;
+    p.m = m; p.n = n; p.k = k;
+    stream_geometry(m, k, c, nt, &p);
+    p.status = d.status;
+    p.counters = (unsigned int *)d.scratch;
+    p.partials = (float *)((uint8_t *)d.scratch + counters);
+    int ctas = c.ctas;
+    if ((long long)ctas > p.units) ctas = (int)p.units;
+    const size_t smem = stream_smem_bytes(p);
+    for (int tok0 = 0; tok0 < n; tok0 += c.tile_tok) {
+        p.tok0 = tok0;
+        switch (c.rows_per_warp * 10 + nt) {
+            case 11: st = launch_one<1, 1>(p, ctas, smem, (cudaStream_t)stream); break;
+            case 12: st = launch_one<1, 2>(p, ctas, smem, (cudaStream_t)stream); break;
+            case 14: st = launch_one<1, 4>(p, ctas, smem, (cudaStream_t)stream); break;
+            case 21: st = launch_one<2, 1>(p, ctas, smem, (cudaStream_t)stream); break;
+            case 22: st = launch_one<2, 2>(p, ctas, smem, (cudaStream_t)stream); break;
+            default: return TUNA_ERR_BAD_CONFIG;
+        }
+        if (st != TUNA_OK) return st;
+    }
+    return TUNA_OK;
+}

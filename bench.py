@@ -112,24 +112,26 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------- CPU reference arm
 
-def cpu_reference_step(shapes, tokens, reps, oracle):
-    """dequantize (C oracle, all host threads) + torch.matmul (fp16, CPU) for each GEMM of one layer.
-    Returns (seconds per pass, algorithmic bytes per pass, threads)."""
+def cpu_reference_step(shapes, tokens, reps, oracle, layers=1):
+    """dequantize (C oracle, all host threads) + torch.matmul (fp16, CPU) for each GEMM of `layers`
+    layers with distinct weights.  Returns (seconds per pass list, algorithmic bytes per pass, threads)."""
     from oracle import tuna_oracle as orc
 
     rng = np.random.default_rng(0)
     cases = []
-    for _kind, m, k in shapes:
-        q = rng.integers(0, 256, size=m * k // 2, dtype=np.uint8)
-        absmax = (0.005 + 0.015 * rng.random(m, dtype=np.float32)).astype(np.float16).astype(np.float32)
-        x = torch.from_numpy(rng.standard_normal((tokens, k), dtype=np.float32).astype(np.float16))
-        w = np.empty((m, k), dtype=np.uint16)
-        cases.append((m, k, q, absmax, x, w))
+    for _layer in range(layers):
+        for _kind, m, k in shapes:
+            q = rng.integers(0, 256, size=m * k // 2, dtype=np.uint8)
+            absmax = (0.005 + 0.015 * rng.random(m, dtype=np.float32)).astype(np.float16).astype(np.float32)
+            x = torch.from_numpy(rng.standard_normal((tokens, k), dtype=np.float32).astype(np.float16))
+            cases.append((m, k, q, absmax, x))
+    scratch = {(m, k): np.empty((m, k), dtype=np.uint16) for _, m, k in shapes}
     code = orc.NF4_CODE.copy()
     vp = ctypes.c_void_p
 
     def one_pass():
-        for m, k, q, absmax, x, w in cases:
+        for m, k, q, absmax, x in cases:
+            w = scratch[(m, k)]
             oracle.oracle_dequant(q.ctypes.data_as(vp), absmax.ctypes.data_as(vp), code.ctypes.data_as(vp),
                                   w.ctypes.data_as(vp), m, k)
             wt = torch.from_numpy(w.view(np.float16))
@@ -140,7 +142,7 @@ def cpu_reference_step(shapes, tokens, reps, oracle):
         t0 = time.perf_counter()
         one_pass()
         times.append(time.perf_counter() - t0)
-    nbytes = sum(alg_bytes(m, tokens, k) for _, m, k in shapes)
+    nbytes = layers * sum(alg_bytes(m, tokens, k) for _, m, k in shapes)
     return times, nbytes, torch.get_num_threads()
 
 
@@ -156,16 +158,18 @@ def run_reference_arm(args, layers, shapes, tokens):
     if rank != 0:
         return
     oracle = load_oracle_lib()
-    times, nbytes, threads = cpu_reference_step(shapes, tokens, args.warmup + args.steps, oracle)
+    sample_layers = min(layers, 8)
+    times, nbytes, threads = cpu_reference_step(shapes, tokens, args.warmup + args.steps, oracle, sample_layers)
     timed = times[args.warmup:]
     sec = sum(timed) / len(timed)
     gbs = nbytes / sec / 1e9
-    sample = f"one of {layers} layers per step ({len(shapes)} GEMMs, {nbytes / 1e6:.1f} MB algorithmic): C dequant + torch.matmul fp16 on CPU"
+    sample = (f"{sample_layers} of {layers} layers per step, distinct weights ({sample_layers * len(shapes)} GEMMs, {nbytes / 1e6:.1f} MB "
+              "algorithmic): C dequant (all host threads) + torch.matmul fp16 on CPU")
     line = {
         "impl": "reference", "metric": "m16_gemm_effective_hbm_bandwidth", "value": gbs, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16*u4->f32", "data": "synthetic",
-        "config": {"workload": args.workload, "tokens": tokens, "step": "bounded sample: one layer", "timing": "host wall clock"},
+        "config": {"workload": args.workload, "tokens": tokens, "step": f"bounded sample: {sample_layers} layers", "timing": "host wall clock"},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -184,9 +188,12 @@ def main():
     ap.add_argument("--workload", default="mistral7b_mlp_m16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replay")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="use only the first N layers (profiling captures); 0 = all")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     layers, shapes, tokens = WORKLOADS[args.workload]
+    if args.layers > 0:
+        layers = min(layers, args.layers)
 
     if args.impl == "reference":
         run_reference_arm(args, layers, shapes, tokens)
@@ -330,12 +337,14 @@ def main():
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         oracle = load_oracle_lib()
-        times, nbytes, threads = cpu_reference_step(shapes, tokens, 3, oracle)
-        sec = statistics.median(times)
+        sample_layers = min(layers, 8)
+        times, nbytes, threads = cpu_reference_step(shapes, tokens, 4, oracle, sample_layers)
+        sec = statistics.median(times[1:])
         cpu = {"value": nbytes / sec / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-               "sample": f"one of {layers} layers ({len(shapes)} GEMMs, {nbytes / 1e6:.1f} MB algorithmic), median of 3: "
-                         "C restatement of the reference's dequant (all host threads) + torch.matmul fp16 on CPU",
-               "seconds_per_layer": sec}
+               "sample": f"{sample_layers} of {layers} layers with distinct weights ({sample_layers * len(shapes)} GEMMs, "
+                         f"{nbytes / 1e6:.1f} MB algorithmic), median of 3 after 1 warm-up: C restatement of the "
+                         "reference's dequant (all host threads) + torch.matmul fp16 on CPU",
+               "seconds_per_sample": sec}
 
     h2d = layers * sum(t.numel() * 2 for t in x_host)
     d2h = layers * sum(t.numel() * 2 for t in o_host)

@@ -42,8 +42,7 @@
 // Results are bit-identical from run to run, the output needs no zero fill, and there are no
 // floating-point atomics (the reference atomically adds fp16 partials, kernel.cu:2739-2745).
 //
-// The only waits are the rendezvous of the 16 warps at the end of a tile segment; they are
-// bounded (sm100_ptx.cuh): a wait that runs out records where and everybody unwinds.
+// The kernel waits on nothing but its own CTA barrier: no other CTA, no asynchronous engine.
 #include <cstring>
 #include <mutex>
 #include "common.cuh"
@@ -126,14 +125,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
 {
     constexpr int PF = kLoadsInFlight / R;  // steps of weights in flight per warp
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t s_sync_bar;
-    __shared__ int s_abort;
     __shared__ int s_last;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cta = blockIdx.x, ctas = gridDim.x;
     const int WM = p.warps_m, WK = p.warps_k, S = p.ksteps;
-    volatile int *abort_flag = &s_abort;
 
     // Shared memory: the table at the first 64-KB boundary of the shared window, the reduction
     // scratch right behind it.
@@ -144,14 +140,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
     const uint32_t x_pitch = (uint32_t)(64 * S * WK + 64);
     const uint32_t x_buf_bytes = (uint32_t)(NT * 8) * x_pitch;
     const uint32_t xbuf_addr = red_addr + (uint32_t)p.red_bytes;
-    const uint32_t sync_bar = smem_u32(&s_sync_bar);
 
-    if (threadIdx.x == 0) {
-        s_abort = 0;
-        s_last = 0;
-        mbar_init(sync_bar, kStreamWarps);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
+    if (threadIdx.x == 0) s_last = 0;
     // byte -> half2 table: even column = high nibble in the low half; 32 copies, one per bank
     for (int e = warp; e < 256; e += kStreamWarps) {
         const __half hi = __float2half_rn(p.code[e >> 4]);
@@ -187,14 +177,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
     };
     constexpr int kAccRegs = R * 2 * NT * 4;
     float *accf = &acc[0][0][0][0];
-    uint32_t sync_phase = 0;
-    // bounded rendezvous of the 16 warps
+    // Rendezvous of the 16 warps.  A plain CTA barrier: every warp runs the same unit loop, nothing
+    // in this kernel waits on another CTA or on an asynchronous engine, so it cannot stall.  (An
+    // mbarrier-based rendezvous cost about a microsecond per use here.)
     auto warps_sync = [&]() -> bool {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(sync_bar);
-        const bool ok = mbar_wait(sync_bar, sync_phase & 1, abort_flag, p.status, 3);
-        ++sync_phase;
-        return ok;
+        __syncthreads();
+        return true;
     };
 
     // ---- weight prefetch cursor: one block of PF steps ahead of the math, across unit and tile

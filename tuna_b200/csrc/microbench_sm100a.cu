@@ -51,16 +51,31 @@ __global__ void k_mma_sync(float *out, int iters)
     if (s == 123.456f) out[0] = s;
 }
 
-// ---- 2. tcgen05.mma cost: one thread issues `iters` MMAs into one accumulator, then commits
-__global__ void k_umma(int m_tile, int n_tile, int iters, int a_from_tmem, long long *out, int *err)
+// ---- 2. tcgen05.mma cost: warp 1, converged, issues `iters` MMAs (elect.sync picks the lane) into one
+// accumulator, four per loop trip with compile-time operand offsets, then commits.  `per_group` adds what a
+// pipeline stage costs the issuing warp: two waits on barriers that are already complete and two commits.
+static __device__ __forceinline__ uint32_t elect_one()
+{
+    uint32_t e;
+    asm volatile("{ .reg .pred P; elect.sync _|P, 0xffffffff; selp.u32 %0, 1, 0, P; }" : "=r"(e));
+    return e;
+}
+static __device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <int N_TILE, int A_FROM_TMEM>
+__global__ void __launch_bounds__(256, 1) k_umma(int groups, int per_group, long long *out, int *err)
 {
     extern __shared__ __align__(1024) uint8_t sm[];
-    __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) uint64_t bar, bar_stage, bar_ready;
     __shared__ uint32_t tbase;
-    const int warp = threadIdx.x >> 5;
-    for (int i = threadIdx.x; i < 16384; i += blockDim.x) ((uint32_t *)sm)[i] = 0x3c003c00u;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < 40960; i += blockDim.x) ((uint32_t *)sm)[i] = 0x3c003c00u;
     if (threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bar)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bar_stage)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s32(&bar_ready)));
         asm volatile("fence.mbarrier_init.release.cluster;");
     }
     if (warp == 0) {
@@ -71,25 +86,40 @@ __global__ void k_umma(int m_tile, int n_tile, int iters, int a_from_tmem, long 
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tm = tbase;
-    if (threadIdx.x == 0) {
-        const uint32_t idesc = (1u << 4) | ((uint32_t)(n_tile >> 3) << 17) | ((uint32_t)(m_tile >> 4) << 24);
+    if (warp == 1) {
+        constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(N_TILE >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
         auto desc = [](uint32_t a) { return (uint64_t)((a & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61); };
-        const uint64_t bd = desc(s32(sm)), ad = desc(s32(sm + 32768));
+        const uint32_t sbase = s32(sm);
         const long long t0 = clock64();
-        for (int it = 0; it < iters; ++it) {
-            const uint32_t acc = it > 0;
-            if (a_from_tmem)
-                asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(tm), "r"(tm + 256 + (it & 7) * 8), "l"(bd), "r"(idesc), "r"(acc) : "memory");
-            else
-                asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tm), "l"(ad), "l"(bd), "r"(idesc), "r"(acc) : "memory");
+        for (int g = 0; g < groups; ++g) {
+            const uint32_t a_t = tm + 256 + (g & 7) * 32, b_s = sbase + (g & 3) * 32768, a_s = sbase + 131072 + (g & 1) * 16384;
+            if (per_group) {
+                for (int w = 0; w < 2; ++w) {
+                    uint32_t ok = 0;  // parity 1 of a fresh barrier: the wait returns at once
+                    while (!ok) asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 1; selp.u32 %0,1,0,p; }" : "=r"(ok) : "r"(s32(&bar_ready)) : "memory");
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            if (elect_one()) {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint32_t acc = (g | kk) != 0;
+                    if (A_FROM_TMEM)
+                        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(tm), "r"(a_t + kk * 8), "l"(desc(b_s + kk * 32)), "r"(idesc), "r"(acc) : "memory");
+                    else
+                        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tm), "l"(desc(a_s + kk * 32)), "l"(desc(b_s + kk * 32)), "r"(idesc), "r"(acc) : "memory");
+                }
+                if (per_group) { umma_commit(s32(&bar_stage)); umma_commit(s32(&bar_stage)); }
+            }
+            __syncwarp();
         }
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&bar)) : "memory");
+        if (elect_one()) umma_commit(s32(&bar));
         uint32_t ok = 0;
         while (!ok) {
             asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0; selp.u32 %0,1,0,p; }" : "=r"(ok) : "r"(s32(&bar)) : "memory");
             if (clock64() - t0 > 4000000000ll) { *err = 1; break; }
         }
-        if (blockIdx.x == 0) out[0] = clock64() - t0;
+        if (blockIdx.x == 0 && lane == 0) out[0] = clock64() - t0;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -225,19 +255,23 @@ int main()
         printf("[1] mma.sync m16n8k16 f16->f32, 16 warps/SM: %.0f TFLOP/s, %.0f MAC/clk/SM\n", 2 * macs / ms / 1e9, macs / (ms * 1e-3) / sms / 1.9e9);
     }
     {   // 2
-        CK(cudaFuncSetAttribute(k_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
-        const int iters = 2000;
-        for (int a_tmem = 1; a_tmem >= 0; --a_tmem)
-            for (int m : {64, 128})
-                for (int n : {16, 64, 256}) {
-                    k_umma<<<sms, 128, 131072>>>(m, n, iters, a_tmem, lout, derr);
-                    CK(cudaDeviceSynchronize());
-                    long long h;
-                    int he;
-                    cudaMemcpy(&h, lout, 8, cudaMemcpyDeviceToHost);
-                    cudaMemcpy(&he, derr, 4, cudaMemcpyDeviceToHost);
-                    printf("[2] tcgen05.mma kind::f16 M=%3d N=%3d K=16, A from %s: %.1f clk per MMA (timeout flag %d)\n", m, n, a_tmem ? "TMEM" : "smem", (double)h / iters, he);
-                }
+        auto run = [&](auto kern, int n, int a_tmem, int per_group) {
+            CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 170 * 1024));
+            const int groups = 1000;
+            kern<<<sms, 256, 170 * 1024>>>(groups, per_group, lout, derr);
+            CK(cudaDeviceSynchronize());
+            long long h;
+            int he;
+            cudaMemcpy(&h, lout, 8, cudaMemcpyDeviceToHost);
+            cudaMemcpy(&he, derr, 4, cudaMemcpyDeviceToHost);
+            printf("[2] tcgen05.mma kind::f16 M=128 N=%3d K=16, A from %s%s: %.1f clk per MMA (ideal %d; timeout flag %d)\n", n,
+                   a_tmem ? "TMEM" : "smem", per_group ? ", +2 waits +2 commits per 4 MMAs" : "", (double)h / (groups * 4), n / 2, he);
+            return 0;
+        };
+        run(k_umma<16, 1>, 16, 1, 0);   run(k_umma<32, 1>, 32, 1, 0);   run(k_umma<64, 1>, 64, 1, 0);
+        run(k_umma<128, 1>, 128, 1, 0); run(k_umma<256, 1>, 256, 1, 0);
+        run(k_umma<16, 0>, 16, 0, 0);   run(k_umma<64, 0>, 64, 0, 0);   run(k_umma<256, 0>, 256, 0, 0);
+        run(k_umma<16, 1>, 16, 1, 1);   run(k_umma<64, 1>, 64, 1, 1);   run(k_umma<256, 1>, 256, 1, 1);
     }
     {   // 3, 5
         const int iters = 20000, warps = 16;

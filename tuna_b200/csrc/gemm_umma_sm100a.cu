@@ -169,7 +169,7 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
     __shared__ int s_abort;
     __shared__ int s_last;
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
     const int J = p.row_blocks;
     const int SW = p.sw, SX = p.sx, SA = p.sa, ND = p.nd;
     const int ctas = gridDim.x, cta = blockIdx.x;
@@ -221,15 +221,16 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
     PROF_ROLE_BEGIN();
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
-        if (lane == 0) {
-            UnitCursor c;
-            c.init(p, cta, ctas);
-            const int n_rg = p.m >> 3;
-            Ring rw, rx;
-            for (; c.valid(); c.next(p), rw.advance(SW), rx.advance(SX)) {
-                const int rt = c.tile / p.tok_tiles, tt = c.tile - rt * p.tok_tiles;
-                const int sw = rw.idx, sx = rx.idx;
-                if (!mbar_wait(w_empty + 8 * sw, rw.phase ^ 1, abort_flag, p.status, 1)) break;
+        // The whole warp runs the loop and the waits; one elected lane issues the copies.
+        UnitCursor c;
+        c.init(p, cta, ctas);
+        const int n_rg = p.m >> 3;
+        Ring rw, rx;
+        for (; c.valid(); c.next(p), rw.advance(SW), rx.advance(SX)) {
+            const int rt = c.tile / p.tok_tiles, tt = c.tile - rt * p.tok_tiles;
+            const int sw = rw.idx, sx = rx.idx;
+            if (!mbar_wait_warp(w_empty + 8 * sw, rw.phase ^ 1, abort_flag, p.status, 1)) break;
+            if (elect_one_sync()) {
                 int blocks_in = 0;
                 for (int j = 0; j < J; ++j)
                     if ((rt * J + j) * 16 < n_rg) ++blocks_in;
@@ -239,59 +240,63 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
                     tma_load_2d(dst, &tmap_q, c.chunk * 256, (rt * J + j) * 16, w_full + 8 * sw);
                     tma_load_2d(dst + 2048, &tmap_q, c.chunk * 256 + 128, (rt * J + j) * 16, w_full + 8 * sw);
                 }
-                if (!mbar_wait(x_empty + 8 * sx, rx.phase ^ 1, abort_flag, p.status, 2)) break;
+            }
+            __syncwarp();
+            if (!mbar_wait_warp(x_empty + 8 * sx, rx.phase ^ 1, abort_flag, p.status, 2)) break;
+            if (elect_one_sync()) {
                 mbar_expect_tx(x_full + 8 * sx, kXStageBytes);
                 tma_load_2d(xring + (uint32_t)sx * kXStageBytes, &tmap_x, c.chunk * kChunkK, tt * N_TILE, x_full + 8 * sx);
             }
+            __syncwarp();
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issue
-        if (lane == 0) {
-            UnitCursor c;
-            c.init(p, cta, ctas);
-            constexpr uint32_t idesc = make_idesc(N_TILE);
-            Ring rx, ra, rd;
+        // The warp stays converged: every lane executes the loop and the waits, one elected
+        // lane issues the MMAs and commits.  (A single diverged thread running this loop
+        // issued an MMA every 130-290 clocks; the converged warp needs about 43.)
+        UnitCursor c;
+        c.init(p, cta, ctas);
+        constexpr uint32_t idesc = make_idesc(N_TILE);
+        Ring rx, ra, rd;
+        const long long u_first = c.u;
+        for (; c.valid(); c.next(p), rx.advance(SX)) {
+            const bool first = (c.u == u_first) || (c.chunk == 0);
+            const bool last = (c.u + 1 == c.u_end) || (c.chunk + 1 == p.chunks);
+            const int dbuf = rd.idx;
+            if (first) {
+                if (!mbar_wait_warp(d_empty + 8 * dbuf, rd.phase ^ 1, abort_flag, p.status, 3)) break;
+            }
+            const int sx = rx.idx;
+            if (!mbar_wait_warp(x_full + 8 * sx, rx.phase, abort_flag, p.status, 4)) break;
             bool ok = true;
-            const long long u_first = c.u;
-            for (; ok && c.valid(); c.next(p), rx.advance(SX)) {
-                const bool first = (c.u == u_first) || (c.chunk == 0);
-                const bool last = (c.u + 1 == c.u_end) || (c.chunk + 1 == p.chunks);
-                const int dbuf = rd.idx;
-                if (first) {
-                    if (!mbar_wait(d_empty + 8 * dbuf, rd.phase ^ 1, abort_flag, p.status, 3)) break;
-                    tc_fence_after();
-                }
-                const int sx = rx.idx;
-                if (!mbar_wait(x_full + 8 * sx, rx.phase, abort_flag, p.status, 4)) break;
+            Ring rwait = ra;
+            for (int j = 0; j < J; ++j, rwait.advance(SA))
+                if (!mbar_wait_warp(a_full + 8 * rwait.idx, rwait.phase, abort_flag, p.status, 5)) { ok = false; break; }
+            if (!ok) break;
+            tc_fence_after();
+            if (elect_one_sync()) {
                 const uint32_t xbase = xring + (uint32_t)sx * kXStageBytes;
-                // Dependent MMAs (same accumulator) are far slower back to back than independent
-                // ones when N is small, so the unit's J x 4 MMAs are issued k-step-major over
-                // J x k_accs accumulators; the epilogue adds the k_accs partial accumulators.
-                int slots[4];
-                for (int j = 0; j < J; ++j, ra.advance(SA)) {
-                    slots[j] = ra.idx;
-                    if (!mbar_wait(a_full + 8 * ra.idx, ra.phase, abort_flag, p.status, 5)) { ok = false; break; }
-                }
-                if (!ok) break;
-                tc_fence_after();
+                const uint32_t dbase = tmem + (uint32_t)dbuf * d_cols;
+                // The unit's J x 4 MMAs go k-step-major over the J row blocks' accumulators
+                // (x k_accs partial accumulators each, summed by the epilogue).
 #pragma unroll
                 for (int kk = 0; kk < kChunkK / 16; ++kk) {
-                    const int a = kk & (KA - 1);
+                    const uint32_t acc_col = (uint32_t)(kk & (KA - 1)) * N_TILE;
                     const uint64_t bdesc = make_b_desc(xbase + kk * 32);
-                    for (int j = 0; j < J; ++j) {
-                        const uint32_t d_t = tmem + (uint32_t)dbuf * d_cols + (uint32_t)(j * KA + a) * N_TILE;
-                        const uint32_t a_t = a_base + (uint32_t)slots[j] * kSlotCols + kk * 8;
-                        tc_mma_ts(d_t, a_t, bdesc, idesc, (first && kk < KA) ? 0u : 1u);
-                    }
+                    const uint32_t fresh = (first && kk < KA) ? 0u : 1u;
+                    Ring ri = ra;
+                    for (int j = 0; j < J; ++j, ri.advance(SA))
+                        tc_mma_ts(dbase + (uint32_t)(j * KA) * N_TILE + acc_col,
+                                  a_base + (uint32_t)ri.idx * kSlotCols + kk * 8, bdesc, idesc, fresh);
                 }
-                for (int j = 0; j < J; ++j) tc_commit(a_empty + 8 * slots[j]);
-                if (!ok) break;
+                Ring ri = ra;
+                for (int j = 0; j < J; ++j, ri.advance(SA)) tc_commit(a_empty + 8 * ri.idx);
                 tc_commit(x_empty + 8 * sx);
-                if (last) {
-                    tc_commit(d_full + 8 * dbuf);
-                    rd.advance(ND);
-                }
+                if (last) tc_commit(d_full + 8 * dbuf);
             }
+            __syncwarp();
+            ra = rwait;
+            if (last) rd.advance(ND);
         }
     } else if (warp < kFirstDequantWarp) {
         // ------------------------------------------------------------------ epilogue

@@ -75,6 +75,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 #endif
 }
 
+// The same wait executed by a whole converged warp, with one answer for all its lanes.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                               DeviceStatus *status, int where)
+{
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, where)) != 0;
+}
+
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one_sync()
+{
+    uint32_t e;
+    asm volatile("{\n .reg .pred P;\n elect.sync _|P, 0xffffffff;\n selp.u32 %0, 1, 0, P;\n}" : "=r"(e));
+    return e != 0;
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar)
 {
     asm volatile(

@@ -61,10 +61,10 @@ typedef struct tuna_config {
     int32_t k_steps;       /* stream: 32-column steps per warp per unit (8|16|32|64)  */
     int32_t ctas;          /* persistent CTAs (0 = one per SM)                        */
     int32_t stages_w;      /* umma: packed-weight ring depth (64-column stages)       */
-    int32_t stages_x;      /* umma: activation ring depth                             */
+    int32_t stages_x;      /* umma: unit stages (activation tile + A-operand slots)   */
     int32_t dequant_warps; /* umma: warps converting codes into TMEM (mult of 4)      */
     int32_t row_blocks;    /* umma: 128-row blocks per CTA tile (1|2|4)               */
-    int32_t stages_a;      /* umma: TMEM operand slots (32 columns each)              */
+    int32_t stages_a;      /* umma: derived (stages_x * row_blocks TMEM operand slots) */
     int32_t k_accs;        /* umma: accumulators per row block along K (1|2|4)        */
     int32_t reserved[3];
 } tuna_config;

@@ -66,7 +66,7 @@ struct UmmaParams {
     int row_tiles;    // ceil(m / (128 J))
     int tok_tiles;    // ceil(n / tile_tok)
     long long units;  // row_tiles * tok_tiles * C
-    int sw, sx, sa, nd;
+    int sw, sx, nd;
     int k_accs;       // accumulators a K chunk's four MMAs are spread over (1, 2 or 4)
     int dq_groups;
 };
@@ -141,19 +141,20 @@ __host__ __device__ constexpr uint32_t make_idesc(int n_tile)
 __device__ __forceinline__ int lane_row_group(int quarter, int l) { return 8 * (quarter >> 1) + (quarter & 1) + 2 * (l >> 3); }
 
 struct UnitCursor {
-    long long u, u_end;
-    int chunk, tile;
+    int tile, chunk;
+    int left, total;  // units still to do / units of this CTA
     __device__ void init(const UmmaParams &p, int cta, int ctas)
     {
-        u = (p.units * cta) / ctas;
-        u_end = (p.units * (cta + 1)) / ctas;
+        const long long u = (p.units * cta) / ctas, u_end = (p.units * (cta + 1)) / ctas;
         tile = (int)(u / p.chunks);
         chunk = (int)(u - (long long)tile * p.chunks);
+        left = total = (int)(u_end - u);
     }
-    __device__ bool valid() const { return u < u_end; }
+    __device__ bool valid() const { return left > 0; }
+    __device__ bool first_of_segment() const { return left == total || chunk == 0; }
     __device__ void next(const UmmaParams &p)
     {
-        ++u;
+        --left;
         if (++chunk == p.chunks) { chunk = 0; ++tile; }
     }
 };
@@ -171,7 +172,7 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
     const int J = p.row_blocks;
-    const int SW = p.sw, SX = p.sx, SA = p.sa, ND = p.nd;
+    const int SW = p.sw, SX = p.sx, ND = p.nd;
     const int ctas = gridDim.x, cta = blockIdx.x;
 
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem);
@@ -181,10 +182,12 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
 
     // barrier ring bases (indices into bars[])
     const uint32_t bar0 = smem_u32(&bars[0]);
+    // w ring: packed weights (TMA -> dequant warps).  Unit ring: one stage = the unit's activation
+    // tile in shared memory plus its J A-operand slots in tensor memory; `u_full` collects the
+    // activation copy and the 4J dequant warps, `u_empty` is one tcgen05.commit.
     const uint32_t w_full = bar0, w_empty = w_full + 8 * SW;
-    const uint32_t x_full = w_empty + 8 * SW, x_empty = x_full + 8 * SX;
-    const uint32_t a_full = x_empty + 8 * SX, a_empty = a_full + 8 * SA;
-    const uint32_t d_full = a_empty + 8 * SA, d_empty = d_full + 8 * ND;
+    const uint32_t u_full = w_empty + 8 * SW, u_empty = u_full + 8 * SX;
+    const uint32_t d_full = u_empty + 8 * SX, d_empty = d_full + 8 * ND;
     const uint32_t epi_bar = d_empty + 8 * ND;  // the 128 epilogue threads' own barrier
     volatile int *abort_flag = &s_abort;
 
@@ -192,8 +195,7 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
         s_abort = 0;
         s_last = 0;
         for (int i = 0; i < SW; ++i) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, 4 * J); }
-        for (int i = 0; i < SX; ++i) { mbar_init(x_full + 8 * i, 1); mbar_init(x_empty + 8 * i, 1); }
-        for (int i = 0; i < SA; ++i) { mbar_init(a_full + 8 * i, 4); mbar_init(a_empty + 8 * i, 1); }
+        for (int i = 0; i < SX; ++i) { mbar_init(u_full + 8 * i, 1 + 4 * J); mbar_init(u_empty + 8 * i, 1); }
         for (int i = 0; i < ND; ++i) { mbar_init(d_full + 8 * i, 1); mbar_init(d_empty + 8 * i, 4); }
         mbar_init(epi_bar, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -225,10 +227,10 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
         UnitCursor c;
         c.init(p, cta, ctas);
         const int n_rg = p.m >> 3;
-        Ring rw, rx;
-        for (; c.valid(); c.next(p), rw.advance(SW), rx.advance(SX)) {
+        Ring rw, ru;
+        for (; c.valid(); c.next(p), rw.advance(SW), ru.advance(SX)) {
             const int rt = c.tile / p.tok_tiles, tt = c.tile - rt * p.tok_tiles;
-            const int sw = rw.idx, sx = rx.idx;
+            const int sw = rw.idx, su = ru.idx;
             if (!mbar_wait_warp(w_empty + 8 * sw, rw.phase ^ 1, abort_flag, p.status, 1)) break;
             if (elect_one_sync()) {
                 int blocks_in = 0;
@@ -242,10 +244,10 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
                 }
             }
             __syncwarp();
-            if (!mbar_wait_warp(x_empty + 8 * sx, rx.phase ^ 1, abort_flag, p.status, 2)) break;
+            if (!mbar_wait_warp(u_empty + 8 * su, ru.phase ^ 1, abort_flag, p.status, 2)) break;
             if (elect_one_sync()) {
-                mbar_expect_tx(x_full + 8 * sx, kXStageBytes);
-                tma_load_2d(xring + (uint32_t)sx * kXStageBytes, &tmap_x, c.chunk * kChunkK, tt * N_TILE, x_full + 8 * sx);
+                mbar_expect_tx(u_full + 8 * su, kXStageBytes);
+                tma_load_2d(xring + (uint32_t)su * kXStageBytes, &tmap_x, c.chunk * kChunkK, tt * N_TILE, u_full + 8 * su);
             }
             __syncwarp();
         }
@@ -253,30 +255,26 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
         // ------------------------------------------------------------------ MMA issue
         // The warp stays converged: every lane executes the loop and the waits, one elected
         // lane issues the MMAs and commits.  (A single diverged thread running this loop
-        // issued an MMA every 130-290 clocks; the converged warp needs about 43.)
+        // issued an MMA every 130-290 clocks; the converged warp needs about 43.)  The tensor
+        // pipe queues hardly more than one MMA behind the running one, so everything this
+        // loop does besides issuing is kept short: one wait and one commit per unit.
         UnitCursor c;
         c.init(p, cta, ctas);
         constexpr uint32_t idesc = make_idesc(N_TILE);
-        Ring rx, ra, rd;
-        const long long u_first = c.u;
-        for (; c.valid(); c.next(p), rx.advance(SX)) {
-            const bool first = (c.u == u_first) || (c.chunk == 0);
-            const bool last = (c.u + 1 == c.u_end) || (c.chunk + 1 == p.chunks);
-            const int dbuf = rd.idx;
-            if (first) {
-                if (!mbar_wait_warp(d_empty + 8 * dbuf, rd.phase ^ 1, abort_flag, p.status, 3)) break;
-            }
-            const int sx = rx.idx;
-            if (!mbar_wait_warp(x_full + 8 * sx, rx.phase, abort_flag, p.status, 4)) break;
+        Ring ru, rd;
+        for (; c.valid(); c.next(p), ru.advance(SX)) {
+            const bool first = c.first_of_segment();
+            const bool last = (c.left == 1) || (c.chunk + 1 == p.chunks);
+            const int dbuf = rd.idx, su = ru.idx;
             bool ok = true;
-            Ring rwait = ra;
-            for (int j = 0; j < J; ++j, rwait.advance(SA))
-                if (!mbar_wait_warp(a_full + 8 * rwait.idx, rwait.phase, abort_flag, p.status, 5)) { ok = false; break; }
-            if (!ok) break;
+            if (first) ok = mbar_wait(d_empty + 8 * dbuf, rd.phase ^ 1, abort_flag, p.status, 3);
+            ok = ok && mbar_wait(u_full + 8 * su, ru.phase, abort_flag, p.status, 4);
+            if (!__all_sync(0xffffffffu, ok)) break;
             tc_fence_after();
             if (elect_one_sync()) {
-                const uint32_t xbase = xring + (uint32_t)sx * kXStageBytes;
+                const uint32_t xbase = xring + (uint32_t)su * kXStageBytes;
                 const uint32_t dbase = tmem + (uint32_t)dbuf * d_cols;
+                const uint32_t abase = a_base + (uint32_t)(su * J) * kSlotCols;
                 // The unit's J x 4 MMAs go k-step-major over the J row blocks' accumulators
                 // (x k_accs partial accumulators each, summed by the epilogue).
 #pragma unroll
@@ -284,18 +282,14 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
                     const uint32_t acc_col = (uint32_t)(kk & (KA - 1)) * N_TILE;
                     const uint64_t bdesc = make_b_desc(xbase + kk * 32);
                     const uint32_t fresh = (first && kk < KA) ? 0u : 1u;
-                    Ring ri = ra;
-                    for (int j = 0; j < J; ++j, ri.advance(SA))
-                        tc_mma_ts(dbase + (uint32_t)(j * KA) * N_TILE + acc_col,
-                                  a_base + (uint32_t)ri.idx * kSlotCols + kk * 8, bdesc, idesc, fresh);
+                    for (int j = 0; j < J; ++j)
+                        tc_mma_ts(dbase + (uint32_t)(j * KA) * N_TILE + acc_col, abase + (uint32_t)j * kSlotCols + kk * 8,
+                                  bdesc, idesc, fresh);
                 }
-                Ring ri = ra;
-                for (int j = 0; j < J; ++j, ri.advance(SA)) tc_commit(a_empty + 8 * ri.idx);
-                tc_commit(x_empty + 8 * sx);
+                tc_commit(u_empty + 8 * su);
                 if (last) tc_commit(d_full + 8 * dbuf);
             }
             __syncwarp();
-            ra = rwait;
             if (last) rd.advance(ND);
         }
     } else if (warp < kFirstDequantWarp) {
@@ -318,8 +312,7 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
         while (c.valid()) {
             // the segment: units of one tile inside this CTA's range
             const int tile = c.tile, c0 = c.chunk;
-            const long long left = c.u_end - c.u;
-            const int c1 = (int)((long long)(p.chunks - c0) <= left ? p.chunks : c0 + left);
+            const int c1 = (p.chunks - c0 <= c.left) ? p.chunks : c0 + c.left;
             const int rt = tile / p.tok_tiles, tt = tile - rt * p.tok_tiles;
             const bool full = (c0 == 0 && c1 == p.chunks);
             const int dbuf = rd.idx;
@@ -407,7 +400,7 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
             }
             // advance the cursor past this segment
             const int n_adv = c1 - c0;
-            c.u += n_adv;
+            c.left -= n_adv;
             c.chunk += n_adv;
             if (c.chunk == p.chunks) { c.chunk = 0; ++c.tile; }
             rd.advance(ND);
@@ -426,19 +419,19 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
         const uint32_t *lut_lane = lut + lane;
         UnitCursor c;
         c.init(p, cta, ctas);
-        Ring rw, ra;
+        Ring rw, ru;
         int turn = 0;  // task index modulo the number of dequant groups
         bool ok = true;
-        for (; ok && c.valid(); c.next(p), rw.advance(SW)) {
-            const int sw = rw.idx;
+        for (; ok && c.valid(); c.next(p), rw.advance(SW), ru.advance(SX)) {
+            const int sw = rw.idx, su = ru.idx;
             bool waited = false;
-            for (int j = 0; j < J; ++j, ra.advance(SA), turn = (turn + 1 == G) ? 0 : turn + 1) {
+            for (int j = 0; j < J; ++j, turn = (turn + 1 == G) ? 0 : turn + 1) {
                 if (turn != group) continue;
                 if (!waited) {
                     if (!mbar_wait(w_full + 8 * sw, rw.phase, abort_flag, p.status, 7)) { ok = false; break; }
                     waited = true;
                 }
-                const int slot = ra.idx;
+                const int slot = su * J + j;
                 const uint32_t wb = wring + (uint32_t)(sw * J + j) * kWBlockBytes;
                 uint32_t w[8];
 #pragma unroll
@@ -449,14 +442,14 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
                 for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
                     for (int b = 0; b < 4; ++b) v[kt * 4 + b] = lut_lane[((w[kt] >> (8 * b)) & 0xffu) * 32];
-                if (!mbar_wait(a_empty + 8 * slot, ra.phase ^ 1, abort_flag, p.status, 8)) { ok = false; break; }
+                if (!mbar_wait(u_empty + 8 * su, ru.phase ^ 1, abort_flag, p.status, 8)) { ok = false; break; }
                 tc_fence_after();
                 tc_st_x32(a_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)slot * kSlotCols, v);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(a_full + 8 * slot);
+                    mbar_arrive(u_full + 8 * su);
                     mbar_arrive(w_empty + 8 * sw);
                 }
             }
@@ -482,12 +475,12 @@ static int pick_tile_tok(int n)
     return 256;
 }
 
-// Two accumulator buffers (epilogue of one segment overlaps the MMAs of the next) when they
-// leave at least four A-operand slots in the 512 TMEM columns.
+// Two accumulator buffers (the epilogue of one segment overlaps the MMAs of the next) when they
+// leave room for at least two unit stages of A-operand slots in the 512 TMEM columns.
 static int umma_num_dbuf(const tuna_config &c)
 {
     const int dcols = c.row_blocks * c.k_accs * c.tile_tok;
-    return (2 * dcols + 4 * kSlotCols <= kTmemCols) ? 2 : 1;
+    return (2 * dcols + 2 * c.row_blocks * kSlotCols <= kTmemCols) ? 2 : 1;
 }
 
 static size_t umma_smem_bytes(const tuna_config &c)
@@ -505,21 +498,25 @@ int gemm_umma_normalize_config(int m, int n, int k, int sm_count, tuna_config *c
     const int t = c->tile_tok;
     if (t != 16 && t != 32 && t != 64 && t != 128 && t != 256) return TUNA_ERR_BAD_CONFIG;
     if (c->row_blocks == 0) c->row_blocks = (t <= 32) ? 4 : (t <= 64 ? 2 : 1);
-    if (c->row_blocks != 1 && c->row_blocks != 2 && c->row_blocks != 4) return TUNA_ERR_BAD_CONFIG;
+    if (c->row_blocks < 1 || c->row_blocks > 4) return TUNA_ERR_BAD_CONFIG;
     if (c->dequant_warps == 0) c->dequant_warps = 16;
     if (c->dequant_warps % 4 || c->dequant_warps < 4 || c->dequant_warps > kMaxDequantWarps) return TUNA_ERR_BAD_CONFIG;
     if (c->k_accs == 0) c->k_accs = 1;  // measured: spreading a chunk's MMAs over several accumulators is slower
     if (c->k_accs != 1 && c->k_accs != 2 && c->k_accs != 4) return TUNA_ERR_BAD_CONFIG;
     const int dcols = c->row_blocks * c->k_accs * t;
-    if (dcols > 256) return TUNA_ERR_BAD_CONFIG;
+    if (dcols + 2 * c->row_blocks * kSlotCols > kTmemCols) return TUNA_ERR_BAD_CONFIG;
     const int nd = umma_num_dbuf(*c);
-    const int max_sa = (kTmemCols - nd * dcols) / kSlotCols;
-    if (c->stages_a == 0) c->stages_a = max_sa < 8 ? max_sa : 8;
-    if (c->stages_a < 2 || c->stages_a > max_sa) return TUNA_ERR_BAD_CONFIG;
-    if (c->stages_w == 0) c->stages_w = (c->row_blocks == 4) ? 4 : (c->row_blocks == 2 ? 6 : 8);
-    if (c->stages_x == 0) c->stages_x = (t >= 128) ? 4 : 6;
-    if (c->stages_w < 2 || c->stages_x < 2 || c->stages_w > 16 || c->stages_x > 16) return TUNA_ERR_BAD_CONFIG;
-    if (2 * c->stages_w + 2 * c->stages_x + 2 * c->stages_a + 5 > 96) return TUNA_ERR_BAD_CONFIG;
+    // a unit stage = one activation tile in shared memory + row_blocks A slots in tensor memory
+    const int max_by_tmem = (kTmemCols - nd * dcols) / (c->row_blocks * kSlotCols);
+    if (c->stages_w == 0) c->stages_w = (c->row_blocks >= 3) ? 4 : (c->row_blocks == 2 ? 6 : 8);
+    if (c->stages_x == 0) {
+        c->stages_x = max_by_tmem < 6 ? max_by_tmem : 6;
+        while (c->stages_x > 2 && umma_smem_bytes(*c) > 225 * 1024) --c->stages_x;
+    }
+    if (c->stages_x < 2 || c->stages_x > max_by_tmem || c->stages_x > 16) return TUNA_ERR_BAD_CONFIG;
+    if (c->stages_w < 2 || c->stages_w > 16) return TUNA_ERR_BAD_CONFIG;
+    c->stages_a = c->stages_x * c->row_blocks;  // derived: A slots = unit stages x row blocks
+    if (2 * c->stages_w + 2 * c->stages_x + 5 > 96) return TUNA_ERR_BAD_CONFIG;
     if (umma_smem_bytes(*c) > 225 * 1024) return TUNA_ERR_BAD_CONFIG;
     if (c->ctas < 0) return TUNA_ERR_BAD_CONFIG;
     if (c->ctas == 0 || c->ctas > sm_count) c->ctas = sm_count;
@@ -578,7 +575,7 @@ int launch_gemm_umma(const GemmArgs &a, const tuna_config &c)
     p.row_tiles = div_up(a.m, kBlockRows * c.row_blocks);
     p.tok_tiles = div_up(a.n, c.tile_tok);
     p.units = umma_units(a.m, a.n, a.k, c);
-    p.sw = c.stages_w; p.sx = c.stages_x; p.sa = c.stages_a;
+    p.sw = c.stages_w; p.sx = c.stages_x;
     p.nd = umma_num_dbuf(c);
     p.k_accs = c.k_accs;
     p.dq_groups = c.dequant_warps / 4;

@@ -63,16 +63,8 @@ __device__ long long g_prof[32];
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                           DeviceStatus *status, int where)
 {
-#ifdef TUNA_PROFILE
-    // try_wait itself may block for a while, so the profile brackets the whole wait
-    const long long t0 = clock64();
-    const bool r = mbar_try_wait(bar, parity) ? true : mbar_wait_slow(bar, parity, abort_flag, status, where);
-    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_prof[where] += clock64() - t0;
-    return r;
-#else
     if (mbar_try_wait(bar, parity)) return true;
     return mbar_wait_slow(bar, parity, abort_flag, status, where);
-#endif
 }
 
 // The same wait executed by a whole converged warp, with one answer for all its lanes.

@@ -37,10 +37,9 @@ STREAM_SPACE = {
     "k_steps": (4, 8, 16, 32, 64),
 }
 UMMA_SPACE = {
-    "row_blocks": (1, 2, 4),
+    "row_blocks": (1, 2, 3, 4),
     "stages_w": (2, 4, 6, 8),
     "stages_x": (2, 4, 6),
-    "stages_a": (2, 4, 6, 8),
     "dequant_warps": (4, 8, 12, 16),
     "k_accs": (1, 2, 4),
 }

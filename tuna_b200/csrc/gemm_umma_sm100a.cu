@@ -7,14 +7,14 @@
 //
 // One persistent CTA per SM, warp-specialised:
 //   warp 0      producer   TMA: packed weights ([m/8 row groups] x [4k bytes] viewed as a 2-D
-//                          u8 tensor, 128-byte swizzle) and activation tiles ([n] x [k] fp16,
-//                          128-byte swizzle) into mbarrier-tracked shared-memory rings
-//   warp 1      MMA        one thread issues tcgen05.mma (M=128, N=tile_tok, K=16, fp32
+//                          u8 tensor, 128-byte swizzle) into an mbarrier-tracked ring
+//   warp 1      MMA        one elected lane issues tcgen05.mma (M=128, N=tile_tok, K=16, fp32
 //                          accumulate): A from TENSOR MEMORY, B through a shared-memory
 //                          descriptor, D in tensor memory
-//   warps 2-5   epilogue   tcgen05.ld of the accumulator, fp32 scale by absmax, fp16 store,
+//   warp 2      producer   TMA: activation tiles ([n] x [k] fp16, 128-byte swizzle)
+//   warps 3-6   epilogue   tcgen05.ld of the accumulator, fp32 scale by absmax, fp16 store,
 //                          split-K fix-up
-//   warps 6..   dequant    packed bytes (shared memory) -> byte->half2 table lookups ->
+//   warps 7..   dequant    packed bytes (shared memory) -> byte->half2 table lookups ->
 //                          tcgen05.st into the A-operand slots of tensor memory.  A thread owns
 //                          one weight row (= one TMEM lane): a 32-bit word of the packed layout
 //                          is 8 consecutive columns of one row (test.py:58-65), i.e. four
@@ -49,7 +49,8 @@ constexpr int kWBlockBytes = kBlockRows * kChunkK / 2;  // 4096: packed bytes of
 constexpr int kSlotCols = kChunkK / 2;         // 32 TMEM columns hold one block-stage of fp16 A
 constexpr int kUmmaLutBytes = 256 * 32 * 4;
 constexpr int kTmemCols = 512;
-constexpr int kFirstDequantWarp = 6;
+constexpr int kFirstEpilogueWarp = 3;
+constexpr int kFirstDequantWarp = 7;
 constexpr int kMaxDequantWarps = 16;
 constexpr int kMaxThreads = 32 * (kFirstDequantWarp + kMaxDequantWarps);
 
@@ -222,15 +223,17 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
 
     PROF_ROLE_BEGIN();
     if (warp == 0) {
-        // ------------------------------------------------------------------ producer
-        // The whole warp runs the loop and the waits; one elected lane issues the copies.
+        // ------------------------------------------------------------------ weight producer
+        // The whole warp runs the loop and the waits; one elected lane issues the copies.  A
+        // copy costs the issuing warp a few hundred clocks, so the weights and the activations
+        // have a producer warp each and run as far ahead as their own rings allow.
         UnitCursor c;
         c.init(p, cta, ctas);
         const int n_rg = p.m >> 3;
-        Ring rw, ru;
-        for (; c.valid(); c.next(p), rw.advance(SW), ru.advance(SX)) {
-            const int rt = c.tile / p.tok_tiles, tt = c.tile - rt * p.tok_tiles;
-            const int sw = rw.idx, su = ru.idx;
+        Ring rw;
+        for (; c.valid(); c.next(p), rw.advance(SW)) {
+            const int rt = c.tile / p.tok_tiles;
+            const int sw = rw.idx;
             if (!mbar_wait_warp(w_empty + 8 * sw, rw.phase ^ 1, abort_flag, p.status, 1)) break;
             if (elect_one_sync()) {
                 int blocks_in = 0;
@@ -244,6 +247,15 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
                 }
             }
             __syncwarp();
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------------------------------ activation producer
+        UnitCursor c;
+        c.init(p, cta, ctas);
+        Ring ru;
+        for (; c.valid(); c.next(p), ru.advance(SX)) {
+            const int rt = c.tile / p.tok_tiles, tt = c.tile - rt * p.tok_tiles;
+            const int su = ru.idx;
             if (!mbar_wait_warp(u_empty + 8 * su, ru.phase ^ 1, abort_flag, p.status, 2)) break;
             if (elect_one_sync()) {
                 mbar_expect_tx(u_full + 8 * su, kXStageBytes);
@@ -295,7 +307,7 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
     } else if (warp < kFirstDequantWarp) {
         // ------------------------------------------------------------------ epilogue
         const int quarter = warp & 3;
-        const int et = (warp - 2) * 32 + lane;  // 0..127 among the epilogue threads
+        const int et = (warp - kFirstEpilogueWarp) * 32 + lane;  // 0..127 among the epilogue threads
         const int row_in_block = 8 * lane_row_group(quarter, lane) + (lane & 7);
         const int tmem_lane = 32 * quarter + lane;
         UnitCursor c;

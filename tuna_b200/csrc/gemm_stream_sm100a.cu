@@ -142,14 +142,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
     const uint32_t xbuf_addr = red_addr + (uint32_t)p.red_bytes;
 
     if (threadIdx.x == 0) s_last = 0;
-    // byte -> half2 table: even column = high nibble in the low half; 32 copies, one per bank
-    for (int e = warp; e < 256; e += kStreamWarps) {
-        const __half hi = __float2half_rn(p.code[e >> 4]);
-        const __half lo = __float2half_rn(p.code[e & 15]);
-        const uint32_t v = (uint32_t)__half_as_ushort(hi) | ((uint32_t)__half_as_ushort(lo) << 16);
-        asm volatile("st.shared.u32 [%0], %1;" ::"r"(lut_addr + (uint32_t)e * 256 + lane * 4), "r"(v) : "memory");
-    }
-    __syncthreads();
+    // Let the next kernel in the stream start as soon as SMs free up (it waits for this grid to
+    // complete before it touches anything this grid writes, see below).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // this CTA's contiguous range of units
     long long u = (p.units * cta) / ctas;
@@ -291,9 +286,29 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
                 if (active && wk == 0) {
 #pragma unroll
                     for (int i = 0; i < kAccRegs; ++i) accf[i] = 0.f;
-                    for (int s = 0; s < nseg; ++s) {
-                        const float *src = p.partials + (size_t)(2 * (cta_first + s) + (s == 0 ? 1 : 0)) * tile_floats +
-                                           (size_t)wm * kAccRegs * 32 + lane;
+                    // segments in unit order (the sum does not depend on arrival order); the loads of
+                    // several segments are issued before their adds so that L2 latency is paid once per group
+                    auto seg_ptr = [&](int s) {
+                        return p.partials + (size_t)(2 * (cta_first + s) + (s == 0 ? 1 : 0)) * tile_floats +
+                               (size_t)wm * kAccRegs * 32 + lane;
+                    };
+                    constexpr int kFix = kAccRegs >= 16 ? 2 : 4;  // segments in flight (register budget)
+                    int s = 0;
+                    for (; s + kFix <= nseg; s += kFix) {
+                        float v[kFix][kAccRegs];
+#pragma unroll
+                        for (int q = 0; q < kFix; ++q) {
+                            const float *src = seg_ptr(s + q);
+#pragma unroll
+                            for (int i = 0; i < kAccRegs; ++i) v[q][i] = __ldcg(src + i * 32);
+                        }
+#pragma unroll
+                        for (int q = 0; q < kFix; ++q)
+#pragma unroll
+                            for (int i = 0; i < kAccRegs; ++i) accf[i] += v[q][i];
+                    }
+                    for (; s < nseg; ++s) {
+                        const float *src = seg_ptr(s);
 #pragma unroll
                         for (int i = 0; i < kAccRegs; ++i) accf[i] += __ldcg(src + i * 32);
                     }
@@ -360,11 +375,21 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
 
     int xb = 0;
     bool ok = true;
-    if (u < u_end) {
-        stage_x(chunk, 0);
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        ok = warps_sync();
+    // Start-up order: the first weights are already on their way (above; weights and the codebook
+    // are constants).  Everything another kernel may have written - activations, the workspace,
+    // the output - is touched only after the grids this one depends on have completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (u < u_end) stage_x(chunk, 0);
+    // byte -> half2 table: even column = high nibble in the low half; 32 copies, one per bank.
+    // Built while the first activations and weights are in flight.
+    for (int e = warp; e < 256; e += kStreamWarps) {
+        const __half hi = __float2half_rn(p.code[e >> 4]);
+        const __half lo = __float2half_rn(p.code[e & 15]);
+        const uint32_t v = (uint32_t)__half_as_ushort(hi) | ((uint32_t)__half_as_ushort(lo) << 16);
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(lut_addr + (uint32_t)e * 256 + lane * 4), "r"(v) : "memory");
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    ok = warps_sync();
     while (ok && u < u_end) {
         if (u + 1 < u_end) stage_x(chunk + 1 == p.chunks ? 0 : chunk + 1, xb ^ 1);  // next unit, other buffer
         if (active) {
@@ -491,8 +516,19 @@ static int launch_one(const StreamParams &p, int ctas, size_t smem, cudaStream_t
             return TUNA_ERR_NO_DEVICE;
         attr_set[dev] = true;
     }
-    gemm_stream_kernel<R, NT><<<ctas, kStreamThreads, smem, stream>>>(p);
-    return cudaGetLastError() == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
+    // Programmatic dependent launch: this grid may become resident while the previous kernel of
+    // the stream is still draining; the kernel orders itself with griddepcontrol.wait.
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)ctas);
+    lc.blockDim = dim3(kStreamThreads);
+    lc.dynamicSmemBytes = smem;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    return cudaLaunchKernelEx(&lc, gemm_stream_kernel<R, NT>, p) == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
 }
 
 int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)

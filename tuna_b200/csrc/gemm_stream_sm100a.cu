@@ -101,7 +101,7 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32
 }
 
 // 128-bit streaming load under a predicate (zeros when the predicate is false), without a branch.
-__device__ __forceinline__ uint4 ldg_stream_pred(const void *p, bool pred)
+__device__ __forceinline__ uint4 ldg_stream_pred(const void *p, unsigned pred)
 {
     uint4 v;
     asm volatile(
@@ -109,7 +109,7 @@ __device__ __forceinline__ uint4 ldg_stream_pred(const void *p, bool pred)
         " mov.b32 %0, 0;\n mov.b32 %1, 0;\n mov.b32 %2, 0;\n mov.b32 %3, 0;\n"
         " @p ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];\n}"
         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-        : "l"(p), "r"((int)pred));
+        : "l"(p), "r"(pred));
     return v;
 }
 
@@ -125,7 +125,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
 {
     constexpr int PF = kLoadsInFlight / R;  // steps of weights in flight per warp
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ int s_last;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cta = blockIdx.x, ctas = gridDim.x;
@@ -141,16 +140,23 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
     const uint32_t x_buf_bytes = (uint32_t)(NT * 8) * x_pitch;
     const uint32_t xbuf_addr = red_addr + (uint32_t)p.red_bytes;
 
-    if (threadIdx.x == 0) s_last = 0;
     // Let the next kernel in the stream start as soon as SMs free up (it waits for this grid to
     // complete before it touches anything this grid writes, see below).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // this CTA's contiguous range of units
-    long long u = (p.units * cta) / ctas;
-    const long long u_end = (p.units * (cta + 1)) / ctas;
-    int tile = (int)(u / p.chunks);
-    int chunk = (int)(u - (long long)tile * p.chunks);
+    // This CTA's contiguous range of STEPS (one step = every warp's 32 columns; a unit is S of
+    // them): the split is as even as one step allows, whatever the shape.  A range may begin
+    // and end inside a unit; the loads and the math of the steps outside it are masked off.
+    const long long steps_total = p.units * S;
+    const long long g_begin = (steps_total * cta) / ctas;
+    const int n_steps = (int)((steps_total * (cta + 1)) / ctas - g_begin);  // steps of this CTA
+    const int tile_steps = p.chunks * S;                                    // steps of one row tile
+    int tile = (int)(g_begin / tile_steps);
+    const int first_in_tile = (int)(g_begin - (long long)tile * tile_steps);
+    int chunk = first_in_tile / S;
+    // positions below are relative to the first step of the first unit this CTA touches
+    const int r_begin = first_in_tile - chunk * S;  // where in that unit the range begins
+    const int r_end = r_begin + n_steps;
 
     const int wm = warp % WM, wk = warp / WM;
     const int g = lane >> 2, t = lane & 3;
@@ -183,23 +189,27 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
     // ---- weight prefetch cursor: one block of PF steps ahead of the math, across unit and tile
     // boundaries.  next_block() describes the block at the cursor (per row block: this lane's
     // source address and how many of the PF steps are inside the matrix) and advances the cursor.
-    long long pu = u;
-    int ptile = tile, pchunk = chunk, ps0 = 0;
-    auto next_block = [&](const uint8_t *(&src)[R], int (&nvalid)[R]) {
+    int ptile = tile, pchunk = chunk, ps0 = (r_begin / PF) * PF;
+    int ppos = ps0;  // relative position of the cursor's block
+    // next_block() also returns, per row block, the mask of the block's PF steps that are
+    // inside the CTA's range and the matrix (bit j = step j).
+    auto next_block = [&](const uint8_t *(&src)[R], unsigned (&vmask)[R]) {
         const int col = (pchunk * WK + wk) * 32 * S + ps0 * 32 + t * 8;  // this lane's first column
-        int nv = (p.k - col + 31) / 32;                                  // steps whose tile starts before k
-        nv = (pu < u_end && active) ? max(0, min(nv, PF)) : 0;
+        const int nv = (p.k - col + 31) / 32;                            // steps whose tile starts before k
+        const int lo = max(r_begin - ppos, 0);
+        const int hi = active ? min(min(r_end - ppos, PF), nv) : 0;
+        const unsigned window = hi > lo ? ((1u << hi) - 1u) & ~((1u << lo) - 1u) : 0u;
 #pragma unroll
         for (int rr = 0; rr < R; ++rr) {
             const int rg = ptile * (4 * R * WM) + 4 * (wm * R + rr) + (g >> 1);
-            const bool in = rg < n_rg && nv > 0;
-            nvalid[rr] = in ? nv : 0;
+            const bool in = rg < n_rg && window != 0u;
+            vmask[rr] = in ? window : 0u;
             src[rr] = p.q + (in ? (size_t)rg * rg_bytes + (size_t)col * 4 + (g & 1) * 16 : 0);
         }
         ps0 += PF;
+        ppos += PF;
         if (ps0 == S) {
             ps0 = 0;
-            ++pu;
             if (++pchunk == p.chunks) { pchunk = 0; ++ptile; }
         }
     };
@@ -232,7 +242,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
 
     // Everything that follows the last unit of a segment (the units of one tile inside this
     // CTA's range: chunks [c0, c1) of tile seg_tile).
-    auto finish_segment = [&](const int seg_tile, const int c0, const int c1) -> bool {
+    auto finish_segment = [&](const int seg_tile, const int t0, const int t1) -> bool {  // steps [t0, t1) of the tile
         // ---- reduce the warps that share rows: fixed binary tree over wk
         if (WK > 1) {
             for (int half = 1; half < WK; half <<= 1) {
@@ -257,61 +267,56 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
             }
         }
 
-        // ---- a tile cut across CTAs: partials through the workspace, last arriver sums
-        const bool full_tile = (c0 == 0 && c1 == p.chunks);
+        // ---- a tile cut across CTAs: partials through the workspace.  Every warp that holds
+        // sums (wk == 0) handles its own rows alone: it writes its partial, arrives at the counter
+        // of its slice of the tile, and the last warp to arrive there adds the slice's partials in
+        // segment order and stores the rows.  No CTA-wide rendezvous; the other warps go on.
+        const bool full_tile = (t0 == 0 && t1 == tile_steps);
         bool do_store = full_tile;
-        if (!full_tile) {
+        if (!full_tile && active && wk == 0) {
             const size_t tile_floats = (size_t)WM * kAccRegs * 32;
-            if (active && wk == 0) {
-                float *dst = p.partials + (size_t)(2 * cta + (c0 == 0 ? 1 : 0)) * tile_floats + (size_t)wm * kAccRegs * 32 + lane;
+            float *dst = p.partials + (size_t)(2 * cta + (t0 == 0 ? 1 : 0)) * tile_floats + (size_t)wm * kAccRegs * 32 + lane;
 #pragma unroll
-                for (int i = 0; i < kAccRegs; ++i) dst[i * 32] = accf[i];
-            }
+            for (int i = 0; i < kAccRegs; ++i) dst[i * 32] = accf[i];
             __threadfence();
-            if (!warps_sync()) return false;
-            const int cta_first = cta_of_unit((long long)seg_tile * p.chunks, p.units, ctas);
-            const int cta_last = cta_of_unit((long long)(seg_tile + 1) * p.chunks - 1, p.units, ctas);
+            __syncwarp();
+            const int cta_first = cta_of_unit((long long)seg_tile * tile_steps, steps_total, ctas);
+            const int cta_last = cta_of_unit((long long)(seg_tile + 1) * tile_steps - 1, steps_total, ctas);
             const int nseg = cta_last - cta_first + 1;
-            if (threadIdx.x == 0) {
-                const unsigned int old = atomicAdd(&p.counters[seg_tile], 1u);
-                const int is_last = (old == (unsigned)nseg - 1);
-                if (is_last) p.counters[seg_tile] = 0;  // leave the counter clean for the next call
-                s_last = is_last;
-            }
-            if (!warps_sync()) return false;
-            const int is_last = s_last;
-            if (!warps_sync()) return false;  // s_last may be rewritten by the next segment
-            if (is_last) {
+            unsigned int *counter = p.counters + (size_t)seg_tile * kStreamWarps + wm;
+            unsigned int old = 0;
+            if (lane == 0) old = atomicAdd(counter, 1u);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old == (unsigned)nseg - 1) {
+                if (lane == 0) *counter = 0;  // leave the counter clean for the next call
                 __threadfence();
-                if (active && wk == 0) {
 #pragma unroll
-                    for (int i = 0; i < kAccRegs; ++i) accf[i] = 0.f;
-                    // segments in unit order (the sum does not depend on arrival order); the loads of
-                    // several segments are issued before their adds so that L2 latency is paid once per group
-                    auto seg_ptr = [&](int s) {
-                        return p.partials + (size_t)(2 * (cta_first + s) + (s == 0 ? 1 : 0)) * tile_floats +
-                               (size_t)wm * kAccRegs * 32 + lane;
-                    };
-                    constexpr int kFix = kAccRegs >= 16 ? 2 : 4;  // segments in flight (register budget)
-                    int s = 0;
-                    for (; s + kFix <= nseg; s += kFix) {
-                        float v[kFix][kAccRegs];
+                for (int i = 0; i < kAccRegs; ++i) accf[i] = 0.f;
+                // segments in unit order (the sum does not depend on arrival order); the loads of
+                // several segments are issued before their adds so that L2 latency is paid once per group
+                auto seg_ptr = [&](int s) {
+                    return p.partials + (size_t)(2 * (cta_first + s) + (s == 0 ? 1 : 0)) * tile_floats +
+                           (size_t)wm * kAccRegs * 32 + lane;
+                };
+                constexpr int kFix = kAccRegs >= 16 ? 2 : 4;  // segments in flight (register budget)
+                int s = 0;
+                for (; s + kFix <= nseg; s += kFix) {
+                    float v[kFix][kAccRegs];
 #pragma unroll
-                        for (int q = 0; q < kFix; ++q) {
-                            const float *src = seg_ptr(s + q);
+                    for (int q = 0; q < kFix; ++q) {
+                        const float *src = seg_ptr(s + q);
 #pragma unroll
-                            for (int i = 0; i < kAccRegs; ++i) v[q][i] = __ldcg(src + i * 32);
-                        }
-#pragma unroll
-                        for (int q = 0; q < kFix; ++q)
-#pragma unroll
-                            for (int i = 0; i < kAccRegs; ++i) accf[i] += v[q][i];
+                        for (int i = 0; i < kAccRegs; ++i) v[q][i] = __ldcg(src + i * 32);
                     }
-                    for (; s < nseg; ++s) {
-                        const float *src = seg_ptr(s);
 #pragma unroll
-                        for (int i = 0; i < kAccRegs; ++i) accf[i] += __ldcg(src + i * 32);
-                    }
+                    for (int q = 0; q < kFix; ++q)
+#pragma unroll
+                        for (int i = 0; i < kAccRegs; ++i) accf[i] += v[q][i];
+                }
+                for (; s < nseg; ++s) {
+                    const float *src = seg_ptr(s);
+#pragma unroll
+                    for (int i = 0; i < kAccRegs; ++i) accf[i] += __ldcg(src + i * 32);
                 }
                 do_store = true;
             }
@@ -347,14 +352,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
     uint4 ring[PF][R];
     {
         const uint8_t *src[R];
-        int nvalid[R];
-        next_block(src, nvalid);
+        unsigned vmask[R];
+        next_block(src, vmask);
 #pragma unroll
         for (int j = 0; j < PF; ++j)
 #pragma unroll
-            for (int rr = 0; rr < R; ++rr) ring[j][rr] = ldg_stream_pred(src[rr] + j * 128, j < nvalid[rr]);
+            for (int rr = 0; rr < R; ++rr) ring[j][rr] = ldg_stream_pred(src[rr] + j * 128, (vmask[rr] >> j) & 1u);
     }
-    int seg_c0 = chunk;
+    int seg_t0 = first_in_tile;  // where in its tile the current segment began
     zero_acc();
     // Stages the activations of unit (`xchunk`) into buffer `b`: every thread copies 16-byte
     // pieces; tokens >= n and columns >= k are filled with zeros.
@@ -379,36 +384,49 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
     // are constants).  Everything another kernel may have written - activations, the workspace,
     // the output - is touched only after the grids this one depends on have completed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (u < u_end) stage_x(chunk, 0);
+    if (n_steps > 0) stage_x(chunk, 0);
     // byte -> half2 table: even column = high nibble in the low half; 32 copies, one per bank.
-    // Built while the first activations and weights are in flight.
-    for (int e = warp; e < 256; e += kStreamWarps) {
-        const __half hi = __float2half_rn(p.code[e >> 4]);
-        const __half lo = __float2half_rn(p.code[e & 15]);
-        const uint32_t v = (uint32_t)__half_as_ushort(hi) | ((uint32_t)__half_as_ushort(lo) << 16);
-        asm volatile("st.shared.u32 [%0], %1;" ::"r"(lut_addr + (uint32_t)e * 256 + lane * 4), "r"(v) : "memory");
+    // Built while the first activations and weights are in flight.  Warp w writes the entries
+    // w, w + 16, ...: their low nibble is w, their high nibble counts up.
+    {
+        const float cv = p.code[lane & 15];
+        const uint32_t ch = (uint32_t)__half_as_ushort(__float2half_rn(cv));
+        const uint32_t lo16 = __shfl_sync(0xffffffffu, ch, warp & 15) << 16;
+        for (int e = warp; e < 256; e += kStreamWarps) {
+            const uint32_t v = __shfl_sync(0xffffffffu, ch, e >> 4) | lo16;
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(lut_addr + (uint32_t)e * 256 + lane * 4), "r"(v) : "memory");
+        }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     ok = warps_sync();
-    while (ok && u < u_end) {
-        if (u + 1 < u_end) stage_x(chunk + 1 == p.chunks ? 0 : chunk + 1, xb ^ 1);  // next unit, other buffer
+
+    // `pos` is the relative position of the current unit's first step
+    for (int pos = 0; ok && n_steps > 0 && pos < r_end; pos += S) {
+        const int s_lo = max(r_begin - pos, 0), s_hi = min(r_end - pos, S);  // this unit's steps in range
+        const bool last_unit = pos + S >= r_end;
+        if (!last_unit) stage_x(chunk + 1 == p.chunks ? 0 : chunk + 1, xb ^ 1);  // next unit, other buffer
         if (active) {
-            uint32_t xsrc = xbuf_addr + (uint32_t)xb * x_buf_bytes + x_lane;
-            for (int s0 = 0; s0 < S; s0 += PF, xsrc += PF * 64) {
+            const int s_first = (s_lo / PF) * PF;
+            uint32_t xsrc = xbuf_addr + (uint32_t)xb * x_buf_bytes + x_lane + (uint32_t)s_first * 64u;
+            for (int s0 = s_first; s0 < s_hi; s0 += PF, xsrc += PF * 64) {
                 const uint8_t *src[R];
-                int nvalid[R];
-                next_block(src, nvalid);  // the block PF steps ahead of this one
+                unsigned vmask[R];
+                next_block(src, vmask);  // the block PF steps ahead of this one
+                const int jlo = max(s_lo - s0, 0), jhi = min(s_hi - s0, PF);
+                const unsigned cmask = ((1u << jhi) - 1u) & ~((1u << jlo) - 1u);  // this block's steps inside the range
 #pragma unroll
                 for (int j = 0; j < PF; ++j) {
                     uint4 wv[R], xv[NT];
 #pragma unroll
                     for (int rr = 0; rr < R; ++rr) {
                         wv[rr] = ring[j][rr];
-                        ring[j][rr] = ldg_stream_pred(src[rr] + j * 128, j < nvalid[rr]);
+                        ring[j][rr] = ldg_stream_pred(src[rr] + j * 128, (vmask[rr] >> j) & 1u);
                     }
+                    if ((cmask >> j) & 1u) {
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) xv[nt] = lds128(xsrc + j * 64 + (uint32_t)nt * 8u * x_pitch);
-                    compute(wv, xv);
+                        for (int nt = 0; nt < NT; ++nt) xv[nt] = lds128(xsrc + j * 64 + (uint32_t)nt * 8u * x_pitch);
+                        compute(wv, xv);
+                    }
                 }
             }
         }
@@ -416,15 +434,17 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         if (!warps_sync()) break;
         xb ^= 1;
-        const bool seg_end = (chunk + 1 == p.chunks) || (u + 1 == u_end);
-        if (seg_end && !finish_segment(tile, seg_c0, chunk + 1)) break;
-        ++u;
+        const bool seg_end = (chunk + 1 == p.chunks) || last_unit;
+        if (seg_end && !finish_segment(tile, seg_t0, chunk * S + s_hi)) break;
         if (++chunk == p.chunks) { chunk = 0; ++tile; }
-        if (seg_end) seg_c0 = chunk;
+        if (seg_end) seg_t0 = 0;  // a later segment of this CTA starts a tile
     }
 }
 
 // ------------------------------------------------------------------ host side
+
+// one arrival counter per (row tile, warp slice of the tile)
+static size_t stream_counter_bytes(int row_tiles) { return ((size_t)row_tiles * kStreamWarps * 4 + 255) / 256 * 256; }
 
 static void stream_geometry(int m, int k, const tuna_config &c, int nt, StreamParams *p)
 {
@@ -499,7 +519,7 @@ size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &c)
     StreamParams p;
     const int nt = c.tile_tok / 8;
     stream_geometry(m, k, c, nt, &p);
-    const size_t counters = ((size_t)p.row_tiles * 4 + 255) / 256 * 256;
+    const size_t counters = stream_counter_bytes(p.row_tiles);
     const size_t tile_floats = (size_t)c.warps_m * (c.rows_per_warp * 2 * nt * 4) * 32;
     return counters + 2 * (size_t)c.ctas * tile_floats * 4;
 }
@@ -541,13 +561,16 @@ int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)
     stream_geometry(a.m, a.k, cfg, nt, &p);
     p.status = device_status_word();
     if (!p.status) return TUNA_ERR_NO_DEVICE;
-    const size_t counters = ((size_t)p.row_tiles * 4 + 255) / 256 * 256;
+    const size_t counters = stream_counter_bytes(p.row_tiles);
     if (a.workspace == nullptr || a.workspace_bytes < gemm_stream_workspace_bytes(a.m, a.n, a.k, cfg))
         return TUNA_ERR_WORKSPACE;
     p.counters = (unsigned int *)a.workspace;
     p.partials = (float *)((uint8_t *)a.workspace + counters);
     int ctas = cfg.ctas;
-    if ((long long)ctas > p.units) ctas = (int)p.units;
+    {   // no CTA with less than one block of prefetched steps
+        const long long blocks = p.units * (cfg.k_steps / (kLoadsInFlight / cfg.rows_per_warp));
+        if ((long long)ctas > blocks) ctas = (int)blocks;
+    }
     const size_t smem = stream_smem_bytes(p);
 
     for (int tok0 = 0; tok0 < a.n; tok0 += cfg.tile_tok) {
@@ -627,7 +650,7 @@ extern "C" int tuna_matmul_noalloc(const void *q, const void *x, const void *cod
     StreamParams geo;
     stream_geometry(m, k, c, c.tile_tok / 8, &geo);
     // the counters must start at zero; the array keeps whatever the last call (or an aborted one) left
-    const size_t counters = ((size_t)geo.row_tiles * 4 + 255) / 256 * 256;
+    const size_t counters = stream_counter_bytes(geo.row_tiles);
     if (cudaMemsetAsync(d.scratch, 0, counters, (cudaStream_t)stream) != cudaSuccess) return TUNA_ERR_LAUNCH;
     // same parameter block and launch as launch_gemm_stream, with the static arrays in place of a
     // caller workspace and of the allocated status word
@@ -642,7 +665,10 @@ extern "C" int tuna_matmul_noalloc(const void *q, const void *x, const void *cod
     p.counters = (unsigned int *)d.scratch;
     p.partials = (float *)((uint8_t *)d.scratch + counters);
     int ctas = c.ctas;
-    if ((long long)ctas > p.units) ctas = (int)p.units;
+    {
+        const long long blocks = p.units * (c.k_steps / (kLoadsInFlight / c.rows_per_warp));
+        if ((long long)ctas > blocks) ctas = (int)blocks;
+    }
     const size_t smem = stream_smem_bytes(p);
     for (int tok0 = 0; tok0 < n; tok0 += c.tile_tok) {
         p.tok0 = tok0;

@@ -71,6 +71,7 @@ struct StreamParams {
     int ksteps;  // S: 32-column steps per warp per unit, a multiple of the prefetch distance
     int row_tiles, chunks;
     long long units;
+    int steps_q, steps_r;  // units * ksteps = steps_q * CTAs + steps_r: the first steps_r CTAs take steps_q + 1 steps
     int red_bytes;    // shared-memory scratch of the in-CTA reduction
     int x_buf_bytes;  // one activation buffer
 };
@@ -147,12 +148,17 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
     // This CTA's contiguous range of STEPS (one step = every warp's 32 columns; a unit is S of
     // them): the split is as even as one step allows, whatever the shape.  A range may begin
     // and end inside a unit; the loads and the math of the steps outside it are masked off.
-    const long long steps_total = p.units * S;
-    const long long g_begin = (steps_total * cta) / ctas;
-    const int n_steps = (int)((steps_total * (cta + 1)) / ctas - g_begin);  // steps of this CTA
-    const int tile_steps = p.chunks * S;                                    // steps of one row tile
-    int tile = (int)(g_begin / tile_steps);
-    const int first_in_tile = (int)(g_begin - (long long)tile * tile_steps);
+    // (32-bit arithmetic throughout: the 64-bit divisions of a general formula cost a microsecond.)
+    const int g_begin = cta * p.steps_q + min(cta, p.steps_r);
+    const int n_steps = p.steps_q + (cta < p.steps_r ? 1 : 0);  // steps of this CTA
+    const int tile_steps = p.chunks * S;                        // steps of one row tile
+    // the CTA whose range holds step g
+    auto cta_of_step = [&](int gstep) {
+        const int big = p.steps_r * (p.steps_q + 1);
+        return gstep < big ? gstep / (p.steps_q + 1) : p.steps_r + (gstep - big) / p.steps_q;
+    };
+    int tile = g_begin / tile_steps;
+    const int first_in_tile = g_begin - tile * tile_steps;
     int chunk = first_in_tile / S;
     // positions below are relative to the first step of the first unit this CTA touches
     const int r_begin = first_in_tile - chunk * S;  // where in that unit the range begins
@@ -280,8 +286,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
             for (int i = 0; i < kAccRegs; ++i) dst[i * 32] = accf[i];
             __threadfence();
             __syncwarp();
-            const int cta_first = cta_of_unit((long long)seg_tile * tile_steps, steps_total, ctas);
-            const int cta_last = cta_of_unit((long long)(seg_tile + 1) * tile_steps - 1, steps_total, ctas);
+            const int cta_first = cta_of_step(seg_tile * tile_steps);
+            const int cta_last = cta_of_step((seg_tile + 1) * tile_steps - 1);
             const int nseg = cta_last - cta_first + 1;
             unsigned int *counter = p.counters + (size_t)seg_tile * kStreamWarps + wm;
             unsigned int old = 0;
@@ -446,6 +452,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
 // one arrival counter per (row tile, warp slice of the tile)
 static size_t stream_counter_bytes(int row_tiles) { return ((size_t)row_tiles * kStreamWarps * 4 + 255) / 256 * 256; }
 
+// The even split of the steps over the CTAs; false when the step count leaves 32-bit range.
+static bool stream_split_steps(StreamParams *p, int ctas)
+{
+    const long long steps = p->units * p->ksteps;
+    if (steps >= (1ll << 31) || ctas < 1) return false;
+    p->steps_q = (int)(steps / ctas);
+    p->steps_r = (int)(steps % ctas);
+    return true;
+}
+
 static void stream_geometry(int m, int k, const tuna_config &c, int nt, StreamParams *p)
 {
     p->warps_m = c.warps_m; p->warps_k = c.warps_k; p->ksteps = c.k_steps;
@@ -571,6 +587,7 @@ int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)
         const long long blocks = p.units * (cfg.k_steps / (kLoadsInFlight / cfg.rows_per_warp));
         if ((long long)ctas > blocks) ctas = (int)blocks;
     }
+    if (!stream_split_steps(&p, ctas)) return TUNA_ERR_TOO_LARGE;
     const size_t smem = stream_smem_bytes(p);
 
     for (int tok0 = 0; tok0 < a.n; tok0 += cfg.tile_tok) {
@@ -669,6 +686,7 @@ extern "C" int tuna_matmul_noalloc(const void *q, const void *x, const void *cod
         const long long blocks = p.units * (c.k_steps / (kLoadsInFlight / c.rows_per_warp));
         if ((long long)ctas > blocks) ctas = (int)blocks;
     }
+    if (!stream_split_steps(&p, ctas)) return TUNA_ERR_TOO_LARGE;
     const size_t smem = stream_smem_bytes(p);
     for (int tok0 = 0; tok0 < n; tok0 += c.tile_tok) {
         p.tok0 = tok0;

@@ -108,3 +108,94 @@ def matmul_host(x_host, q, s, c, o_host, m: int, n: int, k: int, *, x_dev=None, 
     x_dev.copy_(x_host, non_blocking=True)
     matmul(x_dev, q, s, c, o_dev, m, n, k)
     o_host.copy_(o_dev, non_blocking=True)
+
+
+class HostPipeline:
+    """`matmul` for callers whose activations and outputs live in (pinned) HOST memory, with the
+    copies overlapped with the GEMMs of neighbouring calls.
+
+    Each call copies `x_host` to a device staging slot on a copy-in stream, runs the GEMM on
+    the caller's current stream, and copies the result to `o_host` on a copy-out stream; events
+    order the three and guard the reuse of the `depth` staging slots.  Calls return at once;
+    `join()` makes the current stream wait for every outstanding copy-out (call it before
+    reading `o_host` buffers, followed by a stream or event synchronisation).  Weights, scales
+    and codebook are parameters and stay on the device, as in the reference.
+
+    A sequence `begin(); matmul(...); ...; join()` can be captured into a CUDA graph (the host
+    buffers are then fixed addresses read and written at every replay): `begin()` forks the two
+    copy streams off the capturing stream and forgets slot history from before the capture.
+    """
+
+    def __init__(self, device, max_x_elems: int, max_o_elems: int, depth: int = 4):
+        self.device = torch.device(device)
+        self.depth = int(depth)
+        self.copy_in = torch.cuda.Stream(device=self.device)
+        self.copy_out = torch.cuda.Stream(device=self.device)
+        self._slots = []
+        for _ in range(self.depth):
+            self._slots.append({
+                "x": torch.empty(max_x_elems, dtype=torch.float16, device=self.device),
+                "o": torch.empty(max_o_elems, dtype=torch.float16, device=self.device),
+                "in": torch.cuda.Event(), "gemm": torch.cuda.Event(), "out": torch.cuda.Event(), "used": False,
+            })
+        self._next = 0
+        self._fork = torch.cuda.Event()
+        # the staging memory was allocated on the current stream
+        self.copy_in.wait_stream(torch.cuda.current_stream(self.device))
+        self.copy_out.wait_stream(torch.cuda.current_stream(self.device))
+
+    def matmul(self, x_host, q, s, c, o_host, m: int, n: int, k: int, *, workspace=None, after_gemm=None) -> None:
+        """One GEMM with host activations and output.  `after_gemm(o_dev)` (optional) runs on the
+        compute stream between the GEMM and the copy-out (e.g. an all-reduce of a K-split layer)."""
+        if n * k > self._slots[0]["x"].numel() or n * m > self._slots[0]["o"].numel():
+            raise ValueError("HostPipeline staging slots are smaller than this GEMM's activations or output")
+        if not (x_host.is_pinned() and o_host.is_pinned()):
+            raise ValueError("HostPipeline needs pinned host tensors (pageable copies would serialise)")
+        slot = self._slots[self._next % self.depth]
+        self._next += 1
+        compute = torch.cuda.current_stream(self.device)
+        xd = slot["x"][: n * k].view(n, k)
+        od = slot["o"][: n * m].view(n, m)
+        if slot["used"]:
+            self.copy_in.wait_event(slot["gemm"])  # the slot's previous GEMM has read its activations
+        with torch.cuda.stream(self.copy_in):
+            xd.copy_(x_host, non_blocking=True)
+            slot["in"].record(self.copy_in)
+        compute.wait_event(slot["in"])
+        if slot["used"]:
+            compute.wait_event(slot["out"])        # the slot's previous result has left the device
+        matmul(xd, q, s, c, od, m, n, k, workspace=workspace)
+        if after_gemm is not None:
+            after_gemm(od)
+        slot["gemm"].record(compute)
+        self.copy_out.wait_event(slot["gemm"])
+        with torch.cuda.stream(self.copy_out):
+            o_host.copy_(od, non_blocking=True)
+            slot["out"].record(self.copy_out)
+        slot["used"] = True
+
+    def begin(self) -> None:
+        """Start of a sequence: both copy streams wait for the current stream's work so far, and
+        the staging slots are treated as free (their earlier uses are ordered before that point)."""
+        compute = torch.cuda.current_stream(self.device)
+        self.join()
+        self._fork.record(compute)
+        self.copy_in.wait_event(self._fork)
+        self.copy_out.wait_event(self._fork)
+        for slot in self._slots:
+            slot["used"] = False
+        self._next = 0
+
+    def reset(self) -> None:
+        """Forget every earlier use of the staging slots.  Only when the device is idle (after a
+        synchronisation), e.g. right before capturing a sequence into a CUDA graph."""
+        for slot in self._slots:
+            slot["used"] = False
+        self._next = 0
+
+    def join(self) -> None:
+        """The current stream waits for every copy-out issued so far."""
+        compute = torch.cuda.current_stream(self.device)
+        for slot in self._slots:
+            if slot["used"]:
+                compute.wait_event(slot["out"])

@@ -229,22 +229,19 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
         // have a producer warp each and run as far ahead as their own rings allow.
         UnitCursor c;
         c.init(p, cta, ctas);
-        const int n_rg = p.m >> 3;
         Ring rw;
         for (; c.valid(); c.next(p), rw.advance(SW)) {
             const int rt = c.tile / p.tok_tiles;
             const int sw = rw.idx;
             if (!mbar_wait_warp(w_empty + 8 * sw, rw.phase ^ 1, abort_flag, p.status, 1)) break;
             if (elect_one_sync()) {
-                int blocks_in = 0;
-                for (int j = 0; j < J; ++j)
-                    if ((rt * J + j) * 16 < n_rg) ++blocks_in;
-                mbar_expect_tx(w_full + 8 * sw, (uint32_t)blocks_in * kWBlockBytes);
-                for (int j = 0; j < blocks_in; ++j) {
-                    const uint32_t dst = wring + (uint32_t)(sw * J + j) * kWBlockBytes;
-                    tma_load_2d(dst, &tmap_q, c.chunk * 256, (rt * J + j) * 16, w_full + 8 * sw);
-                    tma_load_2d(dst + 2048, &tmap_q, c.chunk * 256 + 128, (rt * J + j) * 16, w_full + 8 * sw);
-                }
+                // Two copies per unit whatever J is: each takes 128 bytes (32 columns) of all the
+                // unit's 16 J row groups.  Stage layout: [column half][16 J row groups][128 bytes].
+                // Row groups past the end of the matrix are zero-filled and still counted.
+                const uint32_t dst = wring + (uint32_t)(sw * J) * kWBlockBytes;
+                mbar_expect_tx(w_full + 8 * sw, (uint32_t)J * kWBlockBytes);
+                tma_load_2d(dst, &tmap_q, c.chunk * 256, rt * J * 16, w_full + 8 * sw);
+                tma_load_2d(dst + (uint32_t)J * 2048, &tmap_q, c.chunk * 256 + 128, rt * J * 16, w_full + 8 * sw);
             }
             __syncwarp();
         }
@@ -429,6 +426,7 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
         for (int kt = 0; kt < 4; ++kt)
             off[kt] = (uint32_t)rg * 128 + ((uint32_t)((2 * kt + (r >> 2)) ^ (rg & 7)) << 4) + (uint32_t)(r & 3) * 4;
         const uint32_t *lut_lane = lut + lane;
+        const uint32_t half_bytes = (uint32_t)J * 2048;  // one column half of a weight stage
         UnitCursor c;
         c.init(p, cta, ctas);
         Ring rw, ru;
@@ -444,11 +442,11 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
                     waited = true;
                 }
                 const int slot = su * J + j;
-                const uint32_t wb = wring + (uint32_t)(sw * J + j) * kWBlockBytes;
+                const uint32_t wb = wring + (uint32_t)(sw * J) * kWBlockBytes + (uint32_t)j * 2048;
                 uint32_t w[8];
 #pragma unroll
                 for (int kt = 0; kt < 8; ++kt)
-                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[kt]) : "r"(wb + (kt >> 2) * 2048 + off[kt & 3]));
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[kt]) : "r"(wb + (uint32_t)(kt >> 2) * half_bytes + off[kt & 3]));
                 uint32_t v[32];
 #pragma unroll
                 for (int kt = 0; kt < 8; ++kt)
@@ -605,9 +603,9 @@ int launch_gemm_umma(const GemmArgs &a, const tuna_config &c)
     p.partials = (float *)((uint8_t *)a.workspace + counters);
 
     CUtensorMap mq, mx;
-    // packed weights as [m/8 row groups][4k bytes]; box = 16 row groups x 128 bytes (32 columns)
+    // packed weights as [m/8 row groups][4k bytes]; box = the unit's 16 x row_blocks row groups x 128 bytes (32 columns)
     if (!make_tensor_map_2d(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.q, (uint64_t)a.k * 4, (uint64_t)a.m / 8,
-                            (uint64_t)a.k * 4, 128, 16, CU_TENSOR_MAP_SWIZZLE_128B))
+                            (uint64_t)a.k * 4, 128, 16u * (uint32_t)c.row_blocks, CU_TENSOR_MAP_SWIZZLE_128B))
         return TUNA_ERR_NO_DEVICE;
     // activations as [n][k] fp16; box = tile_tok tokens x 64 columns
     if (!make_tensor_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.x, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.k * 2,

@@ -156,7 +156,8 @@ def load_oracle_lib():
 def run_reference_arm(args, layers, shapes, tokens):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
-        return
+        sys.stdout.flush()
+        os._exit(0)  # nothing left to do; skip the interpreter's teardown of CUDA graphs and NCCL state
     oracle = load_oracle_lib()
     sample_layers = min(layers, 8)
     times, nbytes, threads = cpu_reference_step(shapes, tokens, args.warmup + args.steps, oracle, sample_layers)
@@ -175,6 +176,9 @@ def run_reference_arm(args, layers, shapes, tokens):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+    if world > 1:
+        sys.stdout.flush()
+        os._exit(0)
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -215,6 +219,16 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        # a rank that stops answering must not hold the whole job: give up after a bounded time
+        limit = float(os.environ.get("TUNA_BENCH_WATCHDOG_S", "420"))
+
+        def _give_up():
+            print(json.dumps({"error": f"rank {rank}: multi-GPU bench exceeded {limit:.0f} s, aborted"}), flush=True)
+            os._exit(2)
+
+        watchdog = threading.Timer(limit, _give_up)
+        watchdog.daemon = True
+        watchdog.start()
     lib = _lib.load()
 
     # ---- synthetic weights: uniform-random codes (random bytes), scales U[0.005, 0.02] rounded to fp16
@@ -246,15 +260,22 @@ def main():
     ws = torch.zeros(max(ws_bytes, 1 << 20), dtype=torch.uint8, device=dev)
     stream = torch.cuda.Stream(device=dev)
 
-    def gemm(i, g):
-        tuna_b200.matmul(x_dev[i], g["q"], g["s"], code, o_dev[i], g["m"], tokens, g["k"], workspace=ws)
-        if g["kind"] == "row" and world > 1:
-            dist.all_reduce(o_dev[i])
+    # K-split layers: every layer has its own output so that its all-reduce (NCCL's stream) can stay
+    # in flight under the next layers' GEMMs; the step ends when the last reduction has finished
+    o_layer = None
+    if world > 1:
+        o_layer = [[torch.empty_like(o_dev[i]) if g["kind"] == "row" else None for i, g in enumerate(per)] for per in gemms]
 
     def step_device():
-        for per in gemms:
+        pending = []
+        for li, per in enumerate(gemms):
             for i, g in enumerate(per):
-                gemm(i, g)
+                out = o_layer[li][i] if (o_layer is not None and o_layer[li][i] is not None) else o_dev[i]
+                tuna_b200.matmul(x_dev[i], g["q"], g["s"], code, out, g["m"], tokens, g["k"], workspace=ws)
+                if g["kind"] == "row" and world > 1:
+                    pending.append(dist.all_reduce(out, async_op=True))
+        for h in pending:
+            h.wait()
 
     # end to end: every GEMM takes its activations from pinned HOST memory and returns its output
     # there, through the package's host-buffer API (copies on their own streams, overlapped with
@@ -352,10 +373,16 @@ def main():
         "timing": "isolated back-to-back launches over the layers' distinct weights, CUDA events",
     }
 
+    # Every rank is done with the process group at the same point, before rank 0 goes on alone.
+    # The group is not destroyed: tearing down a communicator that a live CUDA graph still refers
+    # to blocks, so the processes leave with os._exit once their output is flushed.
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        sys.stdout.flush()
+        os._exit(0)  # nothing left to do; skip the interpreter's teardown of CUDA graphs and NCCL state
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -396,7 +423,8 @@ def main():
     }
     print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of the dominant kernel

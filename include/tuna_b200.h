@@ -146,7 +146,22 @@ const char *tuna_status_string(int status);
 int tuna_abi_version(void);
 int tuna_config_table_size(void);
 
+/* Status of the calling thread's last wrapper() / dequantize_wrapper() call (below). */
+int tuna_last_wrapper_status(void);
+
 #ifdef __cplusplus
 }
+
+/*
+ * The reference's own two native entry points, with their C++ linkage and parameter lists
+ * (declared in extension.cpp:22-24, defined in kernel.cu:3009 and kernel.cu:3243), so that the
+ * reference's pybind module links against this library unchanged.  `wrapper` takes its scratch
+ * from a per-device allocation cached inside the library (grown on demand, zero-filled once);
+ * neither function reports errors (the reference's do not either): read
+ * tuna_last_wrapper_status() after the call.
+ */
+struct CUstream_st;
+void wrapper(void *q, void *x, void *c, void *s, void *o, int m, int n, int k, CUstream_st *stream);
+void dequantize_wrapper(void *q, void *a, void *c, void *o, const int m, const int k, CUstream_st *stream);
 #endif
 #endif /* TUNA_B200_H */

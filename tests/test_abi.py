@@ -14,9 +14,24 @@ def test_every_declared_symbol_is_exported(tuna_lib):
     header = (ROOT / "include" / "tuna_b200.h").read_text()
     declared = set(re.findall(r"\b(tuna_[a-z_0-9]+)\s*\(", header))
     assert declared, "no declarations found"
-    assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
+    c_symbols = {n for n in _lib.SYMBOLS if n.startswith("tuna_")}
+    assert declared == c_symbols, declared ^ c_symbols
     for name in declared:
         assert hasattr(tuna_lib, name), name
+
+
+def test_reference_named_cxx_symbols_are_exported(tuna_lib):
+    # the two native symbols the reference's pybind module links against (extension.cpp:22-24)
+    header = (ROOT / "include" / "tuna_b200.h").read_text()
+    assert re.search(r"^void wrapper\(void \*q, void \*x, void \*c, void \*s, void \*o, int m, int n, int k,", header, re.M)
+    assert re.search(r"^void dequantize_wrapper\(void \*q, void \*a, void \*c, void \*o, const int m, const int k,", header, re.M)
+    mangled = [n for n in _lib.SYMBOLS if n.startswith("_Z")]
+    assert sorted(mangled) == ["_Z18dequantize_wrapperPvS_S_S_iiP11CUstream_st", "_Z7wrapperPvS_S_S_S_iiiP11CUstream_st"]
+    for name in mangled:
+        assert hasattr(tuna_lib, name), name
+    # bad shape: nothing is launched, the status says why (no GPU needed)
+    tuna_lib._Z7wrapperPvS_S_S_S_iiiP11CUstream_st(None, None, None, None, None, 60, 1, 64, None)
+    assert tuna_lib.tuna_last_wrapper_status() == -2
 
 
 def test_struct_layout_matches_header():

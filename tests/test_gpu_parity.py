@@ -224,3 +224,22 @@ def test_python_mirror_matches_c_abi():
         tuna_b200.matmul(xd, qd, sd, cd, o, m, n + 1, k)
     with pytest.raises(ValueError):
         tuna_b200.matmul(xd.cpu(), qd, sd, cd, o, m, n, k)
+
+
+def test_reference_named_wrappers_match_the_c_abi():
+    """`wrapper` / `dequantize_wrapper` with the reference's C++ linkage and argument order."""
+    m, n, k = 1024, 16, 2048
+    host, dev = make_case(m, n, k, 21)
+    xd, qd, sd, cd = dev
+    lib = _lib.load()
+    out = torch.full((n, m), float("nan"), dtype=torch.float16, device="cuda")
+    lib._Z7wrapperPvS_S_S_S_iiiP11CUstream_st(qd.data_ptr(), xd.data_ptr(), cd.data_ptr(), sd.data_ptr(), out.data_ptr(),
+                                              m, n, k, stream_ptr())
+    assert lib.tuna_last_wrapper_status() == 0
+    torch.cuda.synchronize()
+    check_parity(out.cpu().numpy(), orc.matmul_ref(*host, m, n, k), TOL)
+    w = torch.empty((m, k), dtype=torch.float16, device="cuda")
+    lib._Z18dequantize_wrapperPvS_S_S_iiP11CUstream_st(qd.data_ptr(), sd.data_ptr(), cd.data_ptr(), w.data_ptr(), m, k, stream_ptr())
+    assert lib.tuna_last_wrapper_status() == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(w.cpu().numpy().view(np.uint16), orc.dequant_ref(host[1], host[2], host[3], m, k).view(np.uint16))

@@ -47,6 +47,10 @@ SYMBOLS = {
     "tuna_status_string": (c_char_p, [c_int]),
     "tuna_abi_version": (c_int, []),
     "tuna_config_table_size": (c_int, []),
+    "tuna_last_wrapper_status": (c_int, []),
+    # the reference's own native symbols (C++ linkage, extension.cpp:22-24), Itanium-mangled
+    "_Z7wrapperPvS_S_S_S_iiiP11CUstream_st": (None, [c_void_p] * 5 + [c_int] * 3 + [c_void_p]),
+    "_Z18dequantize_wrapperPvS_S_S_iiP11CUstream_st": (None, [c_void_p] * 4 + [c_int] * 2 + [c_void_p]),
 }
 
 _lib = None

@@ -140,6 +140,15 @@ int tuna_check_device_status(void *stream);
 int tuna_matmul_noalloc(const void *q, const void *x, const void *code, const void *absmax, void *o,
                         int m, int n, int k, void *stream);
 
+/*
+ * Quantizer: w fp16 [m, k] row-major -> packed codes q [m/8, k/8, 32] + absmax fp32 [m], for the
+ * codebook `code` fp32 [16].  Replaces the reference's quantize_blockwise_dynamic_4bit(w,
+ * block_size = k, preprocess = True) (test.py:7-68, a chain of torch kernels) with two kernels;
+ * bit-identical results: absmax = max |w| per row, code = first index of the nearest codebook
+ * entry to fp32(w) / absmax (fp32 division).  m and k multiples of 8; w and q 16-byte aligned.
+ */
+int tuna_quantize(const void *w, const void *code, void *q, void *absmax, int m, int k, void *stream);
+
 const char *tuna_status_string(int status);
 
 /* Library / table identification: ABI version and number of table entries. */

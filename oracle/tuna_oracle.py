@@ -171,15 +171,20 @@ def quantize_blockwise_dynamic_4bit(w: np.ndarray, code: np.ndarray = NF4_CODE):
         raise ValueError("numel must be a multiple of 128")
     wf = w.astype(np.float32)
     absmax = np.abs(wf).max(axis=1).astype(np.float32)
-    # The reference divides in the input dtype (fp16 tensors in test.py); the
-    # restatement keeps that: the quotient is rounded to the input precision.
-    normalized = (w / absmax.astype(w.dtype)[:, None]).astype(np.float32)
+    # test.py:16-18,42: `absmax` is converted to fp32 before `torch.divide(temp, absmax)`, so
+    # the fp16 weights are promoted and the quotient is an fp32 division (checked against torch
+    # on CPU by tests/golden/make_quantizer_fixture.py).  A row of zeros divides 0 by 0: every
+    # candidate distance is NaN and argmin answers index 0.
+    with np.errstate(divide="ignore", invalid="ignore"):
+        normalized = wf / absmax[:, None]
     codes = np.empty((m, k), dtype=np.uint8)
     rows = max(1, (512 * 1024) // k)
     code32 = np.asarray(code, dtype=np.float32)
     for r0 in range(0, m, rows):
         blk = normalized[r0 : r0 + rows]
-        codes[r0 : r0 + rows] = np.abs(blk[..., None] - code32).argmin(axis=-1)
+        dist = np.abs(blk[..., None] - code32)
+        dist = np.where(np.isnan(dist), np.float32(np.inf), dist)  # all-NaN rows: first index, as torch.argmin
+        codes[r0 : r0 + rows] = dist.argmin(axis=-1)
     return pack_codes(codes), absmax, code32.copy()
 
 

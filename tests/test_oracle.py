@@ -140,3 +140,13 @@ def test_oracle_against_reference_fixtures(path):
         ref = orc.matmul_ref(x, q, absmax, code, m, n, k)
         a, b = orc.parity_error(z["matmul"].view(np.float16), ref)
         assert a <= 1e-2 and b <= 2e-2, (a, b)
+
+
+def test_quantizer_matches_torch_cpu_fixture():
+    """The quantizer restatement against outputs of the reference's torch expression evaluated on
+    the CPU (tests/golden/make_quantizer_fixture.py): a zero row, a constant row, exact midpoints."""
+    d = np.load(GOLDEN / "quantizer_torch_cpu.npz")
+    w = d["w_bits"].view(np.float16)
+    q, absmax, _ = orc.quantize_blockwise_dynamic_4bit(w)
+    assert np.array_equal(absmax, d["absmax"])
+    assert np.array_equal(q, d["q"])

@@ -43,6 +43,7 @@ SYMBOLS = {
     "tuna_matmul_noalloc": (c_int, [c_void_p] * 5 + [c_int] * 3 + [c_void_p]),
     "tuna_lookup_config": (c_int, [c_int] * 3 + [ctypes.POINTER(TunaConfig)]),
     "tuna_dequant": (c_int, [c_void_p] * 4 + [c_int] * 2 + [c_void_p]),
+    "tuna_quantize": (c_int, [c_void_p] * 4 + [c_int] * 2 + [c_void_p]),
     "tuna_check_device_status": (c_int, [c_void_p]),
     "tuna_status_string": (c_char_p, [c_int]),
     "tuna_abi_version": (c_int, []),

@@ -28,6 +28,8 @@ int read_device_status(cudaStream_t stream);
 bool make_tensor_map_2d(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t inner, uint64_t outer,
                         uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle);
 
+cudaError_t launch_quantize(const void *w, const void *code, void *q, void *absmax, int m, int k, int sm_count,
+                            cudaStream_t stream);
 cudaError_t launch_dequant(const void *q, const void *absmax, const void *code, void *o, int m,
                            int k, int sm_count, cudaStream_t stream);
 

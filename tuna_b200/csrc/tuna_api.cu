@@ -143,6 +143,16 @@ extern "C" int tuna_dequant(const void *q, const void *absmax, const void *code,
     return e == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
 }
 
+extern "C" int tuna_quantize(const void *w, const void *code, void *q, void *absmax, int m, int k, void *stream)
+{
+    if (!w || !code || !q || !absmax) return TUNA_ERR_NULL_POINTER;
+    int st = check_shape(m, 1, k);
+    if (st != TUNA_OK) return st;
+    if (!aligned(w, 16) || !aligned(q, 16) || !aligned(absmax, 4) || !aligned(code, 4)) return TUNA_ERR_MISALIGNED;
+    cudaError_t e = launch_quantize(w, code, q, absmax, m, k, device_sm_count(), (cudaStream_t)stream);
+    return e == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
+}
+
 extern "C" int tuna_check_device_status(void *stream) { return read_device_status((cudaStream_t)stream); }
 
 extern "C" const char *tuna_status_string(int s)

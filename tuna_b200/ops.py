@@ -96,6 +96,28 @@ def dequant(q, absmax, codebook, o, m: int, k: int) -> None:
                                        m, k, _stream_ptr(dev)))
 
 
+def quantize(w, codebook=None):
+    """Row-wise absmax quantizer + packer on the device: the reference's
+    `quantize_blockwise_dynamic_4bit(w, block_size=k, preprocess=True)` (test.py:7-68) with the
+    same return structure `(q, (absmax, code))`: `q` uint8 `[m/8, k/8, 32]`, `absmax` fp32 `[m]`,
+    `code` fp32 `[16]` (NF4 unless `codebook` is given)."""
+    from .codebooks import nf4_tensor
+
+    if not isinstance(w, torch.Tensor) or not w.is_cuda:
+        raise ValueError("w must be a CUDA tensor (there is no CPU path)")
+    if w.dtype != torch.float16 or w.dim() != 2 or not w.is_contiguous():
+        raise ValueError("w must be a contiguous fp16 [m, k] tensor")
+    m, k = w.shape
+    code = nf4_tensor(w.device) if codebook is None else codebook
+    _expect(code, "codebook", torch.float32, 16, w.device)
+    q = torch.empty((m // 8, k // 8, 32), dtype=torch.uint8, device=w.device)
+    absmax = torch.empty((m,), dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        check(_lib.load().tuna_quantize(w.data_ptr(), code.data_ptr(), q.data_ptr(), absmax.data_ptr(), m, k,
+                                        _stream_ptr(w.device)))
+    return q, (absmax, code)
+
+
 def matmul_host(x_host, q, s, c, o_host, m: int, n: int, k: int, *, x_dev=None, o_dev=None) -> None:
     """The op with HOST activations and output: copies x (pinned host) to the device, runs the
     GEMM against the resident weights and copies the result back, all on the current stream.

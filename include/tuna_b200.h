@@ -141,6 +141,21 @@ int tuna_matmul_noalloc(const void *q, const void *x, const void *code, const vo
                         int m, int n, int k, void *stream);
 
 /*
+ * `batch` independent GEMMs of one shape in one call: matrix b uses q + b*q_stride,
+ * x + b*x_stride (0 = the same activations for all), absmax + b*absmax_stride and writes
+ * o + b*o_stride (strides in bytes, multiples of 16; `code` is shared).  For token counts of the
+ * streaming kernel (n <= 32) this is ONE launch whose work split runs across the matrices, so
+ * the fixed cost per launch is paid once: the Mixtral expert projections (8 GEMMs of
+ * 14336 -> 4096, per-expert activations) or the reference's "combined" 14336 -> 32768 GEMM
+ * (make_configs.py:105-106, README.md:18: x_stride = 0).  Larger n: one launch per matrix.
+ * Workspace: tuna_matmul_batched_workspace_bytes (zero before the first use, left clean).
+ */
+int tuna_matmul_batched(const void *q, const void *x, const void *code, const void *absmax, void *o,
+                        int m, int n, int k, int batch, size_t q_stride, size_t x_stride, size_t absmax_stride,
+                        size_t o_stride, void *workspace, size_t workspace_bytes, void *stream);
+size_t tuna_matmul_batched_workspace_bytes(int m, int n, int k, int batch);
+
+/*
  * Quantizer: w fp16 [m, k] row-major -> packed codes q [m/8, k/8, 32] + absmax fp32 [m], for the
  * codebook `code` fp32 [16].  Replaces the reference's quantize_blockwise_dynamic_4bit(w,
  * block_size = k, preprocess = True) (test.py:7-68, a chain of torch kernels) with two kernels;

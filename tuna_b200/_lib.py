@@ -40,6 +40,8 @@ SYMBOLS = {
     "tuna_matmul": (c_int, [c_void_p] * 5 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),
     "tuna_matmul_cfg": (c_int, [c_void_p] * 5 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p, ctypes.POINTER(TunaConfig)]),
     "tuna_matmul_workspace_bytes": (c_size_t, [c_int] * 3),
+    "tuna_matmul_batched": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_size_t] * 4 + [c_void_p, c_size_t, c_void_p]),
+    "tuna_matmul_batched_workspace_bytes": (c_size_t, [c_int] * 4),
     "tuna_matmul_noalloc": (c_int, [c_void_p] * 5 + [c_int] * 3 + [c_void_p]),
     "tuna_lookup_config": (c_int, [c_int] * 3 + [ctypes.POINTER(TunaConfig)]),
     "tuna_dequant": (c_int, [c_void_p] * 4 + [c_int] * 2 + [c_void_p]),

@@ -5,16 +5,18 @@
 // mma orientation (weights are the m16 "A" operand, tokens the n8 "B" operand,
 // kernel.cu:2182-2192) and nothing else.
 //
-// Why mma.sync here and not tcgen05: measured on B200, a tcgen05.mma with K=16 takes
-// ~128 clocks whatever M and N are, i.e. at most 16 (weights as M=128) to 32 (weights as
-// N=256) weights per clock per SM, below what HBM delivers (46 per clock per SM);
-// mma.sync.m16n8k16 sustains ~990 MAC/clk/SM = 62 weights per clock at 16 tokens.  The
-// tensor-memory kernel takes over for large token counts.
+// Why mma.sync here and not tcgen05: measured on B200, one tcgen05.mma (M=128, K=16, A from
+// tensor memory) costs its issuing warp at least ~43 clocks whatever N is.  With the weights as
+// the M=128 operand and 16 tokens as N that is 2048 weights per 43 clocks = 47 per clock per SM
+// with nothing else in the issuing warp's loop (27 with a pipeline's waits and commits), no
+// better than what HBM delivers (47 per clock per SM); mma.sync.m16n8k16 on 16 warps sustains
+// 45.6 weights per clock at 16 tokens without a single serial issuer.  The tensor-memory
+// kernel takes over for large token counts.
 //
 // Data movement, also chosen by measurement on B200 in this kernel's access pattern (a warp
 // load = four 128-byte runs, one per row group): 128-bit ld.global straight into a register
-// ring, eight loads in flight per lane, reaches 5.6 TB/s; cp.async into shared memory stops at
-// 2.5 TB/s and TMA boxes of short strided rows at ~3 TB/s.  So every warp streams its own
+// ring, eight loads in flight per lane, reaches 5.8 TB/s; cp.async into shared memory stops at
+// 2.7 TB/s and TMA boxes of short strided rows at ~3 TB/s.  So every warp streams its own
 // weights into registers.  The activations of a unit (tile_tok tokens x the unit's columns, a
 // few KB, L2 resident) are staged in shared memory by all warps with cp.async, one unit ahead,
 // double buffered; the warps meet once per unit.
@@ -34,15 +36,24 @@
 // once, in fp32, to the accumulated sum.
 //
 // Work decomposition.  One persistent CTA per SM, 16 warps arranged warps_m x warps_k.  A
-// "unit" is (row tile of 32*R*warps_m rows, K chunk of 32*S*warps_k columns); units are
-// numbered tile-major and cut into one contiguous range per CTA ("stream-K"), so every SM
-// streams the same number of bytes whatever the shape.  Warps that share rows reduce through
-// shared memory in a fixed tree; a tile cut across CTAs is finished by the CTA that arrives
-// last at the tile's counter, which adds the fp32 partials from the workspace in unit order.
-// Results are bit-identical from run to run, the output needs no zero fill, and there are no
-// floating-point atomics (the reference atomically adds fp16 partials, kernel.cu:2739-2745).
+// "unit" is (row tile of 32*R*warps_m rows, K chunk of 32*S*warps_k columns) and consists of S
+// steps (a step = every warp's next 32 columns).  The steps of all units, tile-major, are cut
+// into one contiguous range per CTA ("stream-K" at step granularity), so every SM streams the
+// same number of bytes whatever the shape; a range may begin and end inside a unit.  Warps
+// that share rows reduce through shared memory in a fixed tree.  A tile cut across CTAs is
+// finished per warp slice: each warp writes its fp32 partial to the workspace and arrives at
+// its slice's counter; the last warp to arrive adds the slice's partials in segment order and
+// stores the rows.  Results are bit-identical from run to run, the output needs no zero fill,
+// and there are no floating-point atomics (the reference atomically adds fp16 partials,
+// kernel.cu:2739-2745).
 //
-// The kernel waits on nothing but its own CTA barrier: no other CTA, no asynchronous engine.
+// Launch.  Programmatic dependent launch: the kernel lets its successor in the stream start
+// at once (griddepcontrol.launch_dependents) and itself waits for its predecessors
+// (griddepcontrol.wait) only after it has requested its first weights; everything another
+// kernel may have produced (activations, workspace, output) is touched after that wait.
+//
+// The kernel waits on nothing but its own CTA barrier and the stream's kernel order: no
+// spinning on other CTAs, no asynchronous engine.
 #include <cstring>
 #include <mutex>
 #include "common.cuh"
@@ -69,7 +80,9 @@ struct StreamParams {
     int tok0;  // first token of this pass
     int warps_m, warps_k;
     int ksteps;  // S: 32-column steps per warp per unit, a multiple of the prefetch distance
-    int row_tiles, chunks;
+    int row_tiles, chunks;  // row tiles of ONE matrix; the tile index runs over batch * row_tiles
+    int batch;              // independent GEMMs of the same shape in this launch (strides below, in bytes)
+    long long q_stride, x_stride, absmax_stride, o_stride;
     long long units;
     int steps_q, steps_r;  // units * ksteps = steps_q * CTAs + steps_r: the first steps_r CTAs take steps_q + 1 steps
     int red_bytes;    // shared-memory scratch of the in-CTA reduction
@@ -157,7 +170,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
         const int big = p.steps_r * (p.steps_q + 1);
         return gstep < big ? gstep / (p.steps_q + 1) : p.steps_r + (gstep - big) / p.steps_q;
     };
-    int tile = g_begin / tile_steps;
+    int tile = g_begin / tile_steps;  // over all matrices of the batch
+    int tile_b = tile / p.row_tiles, tile_rt = tile - tile_b * p.row_tiles;  // matrix, row tile inside it
     const int first_in_tile = g_begin - tile * tile_steps;
     int chunk = first_in_tile / S;
     // positions below are relative to the first step of the first unit this CTA touches
@@ -195,7 +209,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
     // ---- weight prefetch cursor: one block of PF steps ahead of the math, across unit and tile
     // boundaries.  next_block() describes the block at the cursor (per row block: this lane's
     // source address and how many of the PF steps are inside the matrix) and advances the cursor.
-    int ptile = tile, pchunk = chunk, ps0 = (r_begin / PF) * PF;
+    int pb = tile_b, prt = tile_rt, pchunk = chunk, ps0 = (r_begin / PF) * PF;
     int ppos = ps0;  // relative position of the cursor's block
     // next_block() also returns, per row block, the mask of the block's PF steps that are
     // inside the CTA's range and the matrix (bit j = step j).
@@ -207,16 +221,19 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
         const unsigned window = hi > lo ? ((1u << hi) - 1u) & ~((1u << lo) - 1u) : 0u;
 #pragma unroll
         for (int rr = 0; rr < R; ++rr) {
-            const int rg = ptile * (4 * R * WM) + 4 * (wm * R + rr) + (g >> 1);
+            const int rg = prt * (4 * R * WM) + 4 * (wm * R + rr) + (g >> 1);
             const bool in = rg < n_rg && window != 0u;
             vmask[rr] = in ? window : 0u;
-            src[rr] = p.q + (in ? (size_t)rg * rg_bytes + (size_t)col * 4 + (g & 1) * 16 : 0);
+            src[rr] = p.q + (in ? (size_t)pb * (size_t)p.q_stride + (size_t)rg * rg_bytes + (size_t)col * 4 + (g & 1) * 16 : 0);
         }
         ps0 += PF;
         ppos += PF;
         if (ps0 == S) {
             ps0 = 0;
-            if (++pchunk == p.chunks) { pchunk = 0; ++ptile; }
+            if (++pchunk == p.chunks) {
+                pchunk = 0;
+                if (++prt == p.row_tiles) { prt = 0; ++pb; }
+            }
         }
     };
 
@@ -332,9 +349,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
         if (do_store && active && wk == 0) {
 #pragma unroll
             for (int rr = 0; rr < R; ++rr) {
-                const int row = seg_tile * 32 * R * WM + (wm * R + rr) * 32 + 4 * g;
+                const int row = tile_rt * 32 * R * WM + (wm * R + rr) * 32 + 4 * g;  // in matrix tile_b
                 if (row >= p.m) continue;  // m % 8 == 0 and the 4 rows sit inside one 8-row group
-                const float4 sc = *reinterpret_cast<const float4 *>(p.absmax + row);
+                const float4 sc = *reinterpret_cast<const float4 *>(
+                    reinterpret_cast<const uint8_t *>(p.absmax) + (size_t)tile_b * (size_t)p.absmax_stride + (size_t)row * 4);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -344,7 +362,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
                         uint2 v;
                         v.x = pack_half2(acc[rr][0][nt][e] * sc.x, acc[rr][0][nt][2 + e] * sc.y);
                         v.y = pack_half2(acc[rr][1][nt][e] * sc.z, acc[rr][1][nt][2 + e] * sc.w);
-                        *reinterpret_cast<uint2 *>(p.o + (size_t)tok * p.m + row) = v;
+                        *reinterpret_cast<uint2 *>(reinterpret_cast<uint8_t *>(p.o) + (size_t)tile_b * (size_t)p.o_stride +
+                                                   ((size_t)tok * p.m + row) * 2) = v;
                     }
                 }
             }
@@ -370,14 +389,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
     // Stages the activations of unit (`xchunk`) into buffer `b`: every thread copies 16-byte
     // pieces; tokens >= n and columns >= k are filled with zeros.
     const int pieces_per_row = 4 * S * WK;  // 16-byte pieces of one token row of a unit
-    auto stage_x = [&](int xchunk, int b) {
+    auto stage_x = [&](int xbatch, int xchunk, int b) {
+        const __half *xbase = reinterpret_cast<const __half *>(reinterpret_cast<const uint8_t *>(p.x) + (size_t)xbatch * (size_t)p.x_stride);
         const int c0 = xchunk * 32 * S * WK;
         for (int i = threadIdx.x; i < NT * 8 * pieces_per_row; i += kStreamThreads) {
             const int row = i / pieces_per_row, pc = i - row * pieces_per_row;
             const int tok = p.tok0 + row, c = c0 + pc * 8;
             const bool in = tok < p.n && c < p.k;
             cp_async16(xbuf_addr + (uint32_t)b * x_buf_bytes + (uint32_t)row * x_pitch + (uint32_t)pc * 16,
-                       in ? (const void *)(p.x + (size_t)tok * p.k + c) : (const void *)p.x, in ? 16u : 0u);
+                       in ? (const void *)(xbase + (size_t)tok * p.k + c) : (const void *)p.x, in ? 16u : 0u);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -390,7 +410,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
     // are constants).  Everything another kernel may have written - activations, the workspace,
     // the output - is touched only after the grids this one depends on have completed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (n_steps > 0) stage_x(chunk, 0);
+    if (n_steps > 0) stage_x(tile_b, chunk, 0);
     // byte -> half2 table: even column = high nibble in the low half; 32 copies, one per bank.
     // Built while the first activations and weights are in flight.  Warp w writes the entries
     // w, w + 16, ...: their low nibble is w, their high nibble counts up.
@@ -410,7 +430,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
     for (int pos = 0; ok && n_steps > 0 && pos < r_end; pos += S) {
         const int s_lo = max(r_begin - pos, 0), s_hi = min(r_end - pos, S);  // this unit's steps in range
         const bool last_unit = pos + S >= r_end;
-        if (!last_unit) stage_x(chunk + 1 == p.chunks ? 0 : chunk + 1, xb ^ 1);  // next unit, other buffer
+        if (!last_unit) {  // next unit, other buffer
+            const bool wrap = chunk + 1 == p.chunks;
+            stage_x((wrap && tile_rt + 1 == p.row_tiles) ? tile_b + 1 : tile_b, wrap ? 0 : chunk + 1, xb ^ 1);
+        }
         if (active) {
             const int s_first = (s_lo / PF) * PF;
             uint32_t xsrc = xbuf_addr + (uint32_t)xb * x_buf_bytes + x_lane + (uint32_t)s_first * 64u;
@@ -442,7 +465,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
         xb ^= 1;
         const bool seg_end = (chunk + 1 == p.chunks) || last_unit;
         if (seg_end && !finish_segment(tile, seg_t0, chunk * S + s_hi)) break;
-        if (++chunk == p.chunks) { chunk = 0; ++tile; }
+        if (++chunk == p.chunks) {
+            chunk = 0;
+            ++tile;
+            if (++tile_rt == p.row_tiles) { tile_rt = 0; ++tile_b; }
+        }
         if (seg_end) seg_t0 = 0;  // a later segment of this CTA starts a tile
     }
 }
@@ -462,14 +489,15 @@ static bool stream_split_steps(StreamParams *p, int ctas)
     return true;
 }
 
-static void stream_geometry(int m, int k, const tuna_config &c, int nt, StreamParams *p)
+static void stream_geometry(int m, int k, const tuna_config &c, int nt, int batch, StreamParams *p)
 {
+    p->batch = batch;
     p->warps_m = c.warps_m; p->warps_k = c.warps_k; p->ksteps = c.k_steps;
     const int tile_rows = 32 * c.rows_per_warp * c.warps_m;
     const int chunk_cols = 32 * c.k_steps * c.warps_k;
     p->row_tiles = div_up(m, tile_rows);
     p->chunks = div_up(k, chunk_cols);
-    p->units = (long long)p->row_tiles * p->chunks;
+    p->units = (long long)batch * p->row_tiles * p->chunks;
     const int acc_regs = c.rows_per_warp * 2 * nt * 4;
     p->red_bytes = c.warps_k > 1 ? (c.warps_k / 2) * c.warps_m * acc_regs * 128 : 0;
     p->x_buf_bytes = nt * 8 * (chunk_cols * 2 + 64);
@@ -505,7 +533,7 @@ int gemm_stream_normalize_config(int m, int n, int k, int sm_count, tuna_config 
                     if (!c->warps_k)
                         while (t.warps_k > 1 && 32 * t.k_steps * (t.warps_k / 2) >= k) t.warps_k >>= 1;
                     if (t.rows_per_warp * nt > 4 || t.warps_m * t.warps_k > kStreamWarps) continue;
-                    stream_geometry(m, k, t, nt, &p);
+                    stream_geometry(m, k, t, nt, 1, &p);
                     if (stream_smem_bytes(p) > kStreamSmemLimit) continue;
                     const double tile_bytes = (double)t.warps_m * t.rows_per_warp * 32 * nt * 8 * 4;
                     const double cuts = (p.units % c->ctas == 0 && p.chunks % (p.units / c->ctas) == 0) ? 0 : 2.0 * c->ctas;
@@ -523,19 +551,19 @@ int gemm_stream_normalize_config(int m, int n, int k, int sm_count, tuna_config 
     if (c->rows_per_warp * nt > 4) return TUNA_ERR_BAD_CONFIG;  // accumulator registers
     if (!pow2(c->k_steps) || c->k_steps > 64 || c->k_steps % (kLoadsInFlight / c->rows_per_warp)) return TUNA_ERR_BAD_CONFIG;
     if (!pow2(c->warps_m) || !pow2(c->warps_k) || c->warps_m * c->warps_k > kStreamWarps) return TUNA_ERR_BAD_CONFIG;
-    stream_geometry(m, k, *c, nt, &p);
+    stream_geometry(m, k, *c, nt, 1, &p);
     if (stream_smem_bytes(p) > kStreamSmemLimit) return TUNA_ERR_BAD_CONFIG;
     (void)n;
     return TUNA_OK;
 }
 
-size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &c)
+size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &c, int batch)
 {
     (void)n;
     StreamParams p;
     const int nt = c.tile_tok / 8;
-    stream_geometry(m, k, c, nt, &p);
-    const size_t counters = stream_counter_bytes(p.row_tiles);
+    stream_geometry(m, k, c, nt, batch, &p);
+    const size_t counters = stream_counter_bytes(batch * p.row_tiles);
     const size_t tile_floats = (size_t)c.warps_m * (c.rows_per_warp * 2 * nt * 4) * 32;
     return counters + 2 * (size_t)c.ctas * tile_floats * 4;
 }
@@ -574,11 +602,13 @@ int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)
     std::memset(&p, 0, sizeof(p));
     p.q = a.q; p.x = (const __half *)a.x; p.code = a.code; p.absmax = a.absmax; p.o = (__half *)a.o;
     p.m = a.m; p.n = a.n; p.k = a.k;
-    stream_geometry(a.m, a.k, cfg, nt, &p);
+    stream_geometry(a.m, a.k, cfg, nt, a.batch, &p);
+    p.q_stride = (long long)a.q_stride; p.x_stride = (long long)a.x_stride;
+    p.absmax_stride = (long long)a.absmax_stride; p.o_stride = (long long)a.o_stride;
     p.status = device_status_word();
     if (!p.status) return TUNA_ERR_NO_DEVICE;
-    const size_t counters = stream_counter_bytes(p.row_tiles);
-    if (a.workspace == nullptr || a.workspace_bytes < gemm_stream_workspace_bytes(a.m, a.n, a.k, cfg))
+    const size_t counters = stream_counter_bytes(a.batch * p.row_tiles);
+    if (a.workspace == nullptr || a.workspace_bytes < gemm_stream_workspace_bytes(a.m, a.n, a.k, cfg, a.batch))
         return TUNA_ERR_WORKSPACE;
     p.counters = (unsigned int *)a.workspace;
     p.partials = (float *)((uint8_t *)a.workspace + counters);
@@ -665,7 +695,7 @@ extern "C" int tuna_matmul_noalloc(const void *q, const void *x, const void *cod
     const size_t need = gemm_stream_workspace_bytes(m, n, k, c);
     if (need > (size_t)TUNA_NOALLOC_SCRATCH_BYTES) return TUNA_ERR_TOO_LARGE;
     StreamParams geo;
-    stream_geometry(m, k, c, c.tile_tok / 8, &geo);
+    stream_geometry(m, k, c, c.tile_tok / 8, 1, &geo);
     // the counters must start at zero; the array keeps whatever the last call (or an aborted one) left
     const size_t counters = stream_counter_bytes(geo.row_tiles);
     if (cudaMemsetAsync(d.scratch, 0, counters, (cudaStream_t)stream) != cudaSuccess) return TUNA_ERR_LAUNCH;
@@ -677,7 +707,7 @@ extern "C" int tuna_matmul_noalloc(const void *q, const void *x, const void *cod
     p.q = (const uint8_t *)q; p.x = (const __half *)x; p.code = (const float *)code; p.absmax = (const float *)absmax;
     p.o = (__half *)o;
     p.m = m; p.n = n; p.k = k;
-    stream_geometry(m, k, c, nt, &p);
+    stream_geometry(m, k, c, nt, 1, &p);
     p.status = d.status;
     p.counters = (unsigned int *)d.scratch;
     p.partials = (float *)((uint8_t *)d.scratch + counters);

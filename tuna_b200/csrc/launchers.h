@@ -19,6 +19,9 @@ struct GemmArgs {
     size_t workspace_bytes;
     cudaStream_t stream;
     int sm_count;
+    // strided batch of independent GEMMs of one shape (streaming kernel only); strides in bytes
+    int batch = 1;
+    size_t q_stride = 0, x_stride = 0, absmax_stride = 0, o_stride = 0;
 };
 
 struct DeviceStatus;
@@ -35,7 +38,7 @@ cudaError_t launch_dequant(const void *q, const void *absmax, const void *code, 
 
 // mma.sync weight-streaming kernel.  Returns a tuna_status.
 int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg);
-size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &cfg);
+size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &cfg, int batch = 1);
 int gemm_stream_normalize_config(int m, int n, int k, int sm_count, tuna_config *cfg);
 
 // tcgen05/TMEM kernel.  Returns a tuna_status.

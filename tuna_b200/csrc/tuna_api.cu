@@ -109,6 +109,56 @@ extern "C" int tuna_matmul_cfg(const void *q, const void *x, const void *code, c
     return c.path == TUNA_PATH_STREAM ? launch_gemm_stream(a, c) : launch_gemm_umma(a, c);
 }
 
+extern "C" int tuna_matmul_batched(const void *q, const void *x, const void *code, const void *absmax, void *o,
+                                   int m, int n, int k, int batch, size_t q_stride, size_t x_stride, size_t absmax_stride,
+                                   size_t o_stride, void *workspace, size_t workspace_bytes, void *stream)
+{
+    if (!q || !x || !code || !absmax || !o) return TUNA_ERR_NULL_POINTER;
+    int st = check_shape(m, n, k);
+    if (st != TUNA_OK) return st;
+    if (batch < 1 || batch > 65536) return TUNA_ERR_BAD_SHAPE;
+    if (!aligned(q, 16) || !aligned(x, 16) || !aligned(o, 16) || !aligned(absmax, 16) || !aligned(code, 4) ||
+        !aligned(workspace, 16) || (q_stride % 16) || (x_stride % 16) || (absmax_stride % 16) || (o_stride % 16))
+        return TUNA_ERR_MISALIGNED;
+    const int sms = device_sm_count();
+    tuna_config c;
+    st = resolve_config(m, n, k, sms, nullptr, &c);
+    if (st != TUNA_OK) return st;
+    GemmArgs a;
+    a.code = (const float *)code;
+    a.m = m; a.n = n; a.k = k; a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+    a.stream = (cudaStream_t)stream; a.sm_count = sms;
+    if (c.path == TUNA_PATH_STREAM) {
+        // one launch over all matrices: the step range of every CTA runs across them
+        const size_t need = gemm_stream_workspace_bytes(m, n, k, c, batch);
+        if (workspace == nullptr || workspace_bytes < need) return TUNA_ERR_WORKSPACE;
+        a.q = (const uint8_t *)q; a.x = x; a.absmax = (const float *)absmax; a.o = o;
+        a.batch = batch; a.q_stride = q_stride; a.x_stride = x_stride; a.absmax_stride = absmax_stride; a.o_stride = o_stride;
+        return launch_gemm_stream(a, c);
+    }
+    // token counts of the tensor-core kernel: one launch per matrix
+    const size_t need = workspace_for(m, n, k, c, sms);
+    if (workspace == nullptr || workspace_bytes < need) return TUNA_ERR_WORKSPACE;
+    for (int b = 0; b < batch; ++b) {
+        a.q = (const uint8_t *)q + (size_t)b * q_stride;
+        a.x = (const uint8_t *)x + (size_t)b * x_stride;
+        a.absmax = (const float *)((const uint8_t *)absmax + (size_t)b * absmax_stride);
+        a.o = (uint8_t *)o + (size_t)b * o_stride;
+        st = launch_gemm_umma(a, c);
+        if (st != TUNA_OK) return st;
+    }
+    return TUNA_OK;
+}
+
+extern "C" size_t tuna_matmul_batched_workspace_bytes(int m, int n, int k, int batch)
+{
+    if (check_shape(m, n, k) != TUNA_OK || batch < 1) return 0;
+    const int sms = device_sm_count();
+    tuna_config c;
+    if (resolve_config(m, n, k, sms, nullptr, &c) != TUNA_OK) return 0;
+    return c.path == TUNA_PATH_STREAM ? gemm_stream_workspace_bytes(m, n, k, c, batch) : workspace_for(m, n, k, c, sms);
+}
+
 extern "C" int tuna_matmul(const void *q, const void *x, const void *code, const void *absmax, void *o,
                            int m, int n, int k, void *workspace, size_t workspace_bytes, void *stream)
 {

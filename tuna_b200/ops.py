@@ -84,6 +84,37 @@ def matmul(x, q, s, c, o, m: int, n: int, k: int, *, config: TunaConfig | None =
             check(lib.tuna_matmul_cfg(*args, ctypes.byref(config)))
 
 
+def matmul_batched(x, q, s, c, o, m: int, n: int, k: int, *, workspace=None) -> None:
+    """`batch` independent GEMMs of one shape in one call (one launch for n <= 32):
+    `q` uint8 `[batch, m/8, k/8, 32]`, `s` fp32 `[batch, m]`, `o` fp16 `[batch, n, m]`, and `x` fp16
+    either `[batch, n, k]` (per-matrix activations, e.g. one token list per expert) or `[n, k]`
+    (shared: the reference's "combined" Mixtral GEMM, make_configs.py:105-106)."""
+    if not isinstance(q, torch.Tensor) or q.dim() != 4:
+        raise ValueError("q must be a [batch, m/8, k/8, 32] tensor")
+    batch = q.shape[0]
+    dev = q.device
+    _expect(q, "q", torch.uint8, batch * m * k // 2, dev)
+    _expect(s, "s", torch.float32, batch * m, dev)
+    _expect(c, "c", torch.float32, 16, dev)
+    _expect(o, "o", torch.float16, batch * n * m, dev)
+    shared = x.dim() == 2
+    _expect(x, "x", torch.float16, n * k if shared else batch * n * k, dev)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        need = int(lib.tuna_matmul_batched_workspace_bytes(m, n, k, batch))
+        if workspace is None:
+            key = ("batched", dev.index, torch.cuda.current_stream(dev).cuda_stream)
+            ws = _workspaces.get(key)
+            if ws is None or ws.numel() < need:
+                ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+                _workspaces[key] = ws
+        else:
+            ws = workspace
+        check(lib.tuna_matmul_batched(q.data_ptr(), x.data_ptr(), c.data_ptr(), s.data_ptr(), o.data_ptr(), m, n, k, batch,
+                                      m * k // 2, 0 if shared else n * k * 2, m * 4, n * m * 2,
+                                      ws.data_ptr(), ws.numel(), _stream_ptr(dev)))
+
+
 def dequant(q, absmax, codebook, o, m: int, k: int) -> None:
     """`tuna.dequant(q, absmax, codebook, o, m, k)` (extension.cpp:40-49); o fp16 [m,k]."""
     dev = q.device if isinstance(q, torch.Tensor) else None

@@ -45,6 +45,12 @@ WORKLOADS = {
     "mistral7b_mlp_m16": (32, [("col", 28672, 4096), ("row", 4096, 14336)], 16),
     "llama70b_layer_m16": (80, [("col", 10240, 8192), ("row", 8192, 8192), ("col", 57344, 8192), ("row", 8192, 28672)], 16),
     "mistral7b_qkv_m16": (32, [("col", 6144, 4096)], 16),
+    # Mixtral-8x7B expert projections as the reference benchmarks them: one combined GEMM per
+    # projection over all 8 experts (make_configs.py:105-106, README.md:18)
+    "mixtral8x7b_combined_m16": (8, [("col", 229376, 4096), ("row", 32768, 14336)], 16),
+    # token-count sweep of the largest Llama-70B GEMM (one layer each; tensor-core regime from 256 up)
+    "llama70b_gateup_m256": (2, [("col", 57344, 8192)], 256),
+    "llama70b_gateup_m2048": (2, [("col", 57344, 8192)], 2048),
 }
 FALLBACK_HBM_GBS = 6650.0
 
@@ -53,14 +59,14 @@ def alg_bytes(m: int, n: int, k: int) -> int:
     return m * k // 2 + 4 * m + 64 + 2 * n * k + 2 * n * m
 
 
-def measured_peak():
+def measured_peak(key: str = "hbm_gbs", fallback: float = FALLBACK_HBM_GBS):
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         try:
-            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+            return float(json.loads(p.read_text())[key]), "measured"
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback"
+    return fallback, "fallback"
 
 
 class ClockSampler:
@@ -365,13 +371,25 @@ def main():
     peak, peak_kind = measured_peak()
     cfg = tuna_b200.lookup_config(gd["m"], tokens, gd["k"])
     kernel_name = {1: "gemm_stream_kernel (mma.sync)", 2: "gemm_w4a16_umma_kernel (tcgen05)"}[cfg.path]
-    roofline = {
-        "bound": "hbm", "achieved": dom_bytes / (ms_dom * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-        "frac": dom_bytes / (ms_dom * 1e-3) / 1e9 / peak, "traffic": DRAM_TRAFFIC_PER_LAUNCH.get((gd["m"], tokens, gd["k"])),
-        "kernel": kernel_name, "shape": {"m": gd["m"], "n": tokens, "k": gd["k"]}, "us_per_launch": ms_dom * 1e3,
-        "algorithmic_bytes_per_launch": dom_bytes, "peak_source": f"{peak_kind} copy bandwidth",
-        "timing": "isolated back-to-back launches over the layers' distinct weights, CUDA events",
-    }
+    if tokens >= 256:
+        # tensor-bound regime: flops per launch against the measured cuBLAS bf16 burst figure
+        flops = 2.0 * gd["m"] * tokens * gd["k"]
+        tpeak, tkind = measured_peak("bf16_tflops", 1590.0)
+        roofline = {
+            "bound": "tensor", "achieved": flops / (ms_dom * 1e-3) / 1e12, "peak": tpeak, "unit": "TFLOP/s",
+            "frac": flops / (ms_dom * 1e-3) / 1e12 / tpeak, "traffic": None,
+            "kernel": kernel_name, "shape": {"m": gd["m"], "n": tokens, "k": gd["k"]}, "us_per_launch": ms_dom * 1e3,
+            "flops_per_launch": flops, "peak_source": f"{tkind} cuBLAS bf16 burst throughput",
+            "timing": "isolated back-to-back launches over the layers' distinct weights, CUDA events",
+        }
+    else:
+        roofline = {
+            "bound": "hbm", "achieved": dom_bytes / (ms_dom * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+            "frac": dom_bytes / (ms_dom * 1e-3) / 1e9 / peak, "traffic": DRAM_TRAFFIC_PER_LAUNCH.get((gd["m"], tokens, gd["k"])),
+            "kernel": kernel_name, "shape": {"m": gd["m"], "n": tokens, "k": gd["k"]}, "us_per_launch": ms_dom * 1e3,
+            "algorithmic_bytes_per_launch": dom_bytes, "peak_source": f"{peak_kind} copy bandwidth",
+            "timing": "isolated back-to-back launches over the layers' distinct weights, CUDA events",
+        }
 
     # Every rank is done with the process group at the same point, before rank 0 goes on alone.
     # The group is not destroyed: tearing down a communicator that a live CUDA graph still refers

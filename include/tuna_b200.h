@@ -77,12 +77,14 @@ typedef struct tuna_config {
  * `o` is overwritten (no pre-zeroing needed, a pre-zeroed `o` is also fine);
  * every (m % 8 == 0, k % 8 == 0, n >= 1) shape runs instead of only the 14
  * tabulated ones; results are bit-identical from run to run.
- * `workspace` holds split-K partial sums and tile counters; its first
- * tuna_matmul_workspace_bytes() bytes must be ZERO before the first call and
- * are left zeroed-where-needed by every call, so one allocation can be reused
- * by consecutive calls on the same stream (calls that overlap on the device
- * need separate workspaces).  Alignment: q, x, o, workspace 16 bytes; absmax,
- * code 4 bytes.
+ * `workspace` holds split-K partial sums (a region whose size depends only on
+ * the device: about 58 MB on a 148-SM part) followed by arrival counters; its
+ * first tuna_matmul_workspace_bytes() bytes must be ZERO before the first call.
+ * Every call leaves the counters zero and the counters of any shape lie beyond
+ * the partial-sum region, so ONE zero-initialised allocation (sized for the
+ * largest shape) serves consecutive calls of any shapes on one stream; calls
+ * that overlap on the device need separate workspaces.  Alignment: q, x, o,
+ * workspace 16 bytes; absmax, code 4 bytes.
  */
 int tuna_matmul(const void *q, const void *x, const void *code, const void *absmax, void *o,
                 int m, int n, int k, void *workspace, size_t workspace_bytes, void *stream);

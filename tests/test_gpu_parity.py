@@ -243,3 +243,19 @@ def test_reference_named_wrappers_match_the_c_abi():
     assert lib.tuna_last_wrapper_status() == 0
     torch.cuda.synchronize()
     assert np.array_equal(w.cpu().numpy().view(np.uint16), orc.dequant_ref(host[1], host[2], host[3], m, k).view(np.uint16))
+
+
+def test_one_workspace_serves_alternating_shapes_and_kernels():
+    """A single zero-initialised workspace, reused across shapes with different tile counts and
+    across both kernels: the arrival counters of one call never land on another call's partials."""
+    lib = _lib.load()
+    shapes = [(4096, 16, 2048), (256, 16, 8192), (8192, 8, 512), (1024, 64, 1024), (512, 16, 4096), (4096, 16, 2048)]
+    need = max(int(lib.tuna_matmul_workspace_bytes(m, n, k)) for m, n, k in shapes)
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    for rep in range(2):
+        for i, (m, n, k) in enumerate(shapes):
+            host, dev = make_case(m, n, k, 70 + i)
+            st, out, holder = run_matmul(dev, m, n, k, ws=ws)
+            assert st == 0
+            check_parity(out.cpu().numpy(), orc.matmul_ref(*host, m, n, k), TOL)
+            assert holder.guards_intact()

@@ -557,15 +557,14 @@ int gemm_stream_normalize_config(int m, int n, int k, int sm_count, tuna_config 
     return TUNA_OK;
 }
 
-size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &c, int batch)
+size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &c, int sm_count, int batch)
 {
     (void)n;
     StreamParams p;
     const int nt = c.tile_tok / 8;
     stream_geometry(m, k, c, nt, batch, &p);
     const size_t counters = stream_counter_bytes(batch * p.row_tiles);
-    const size_t tile_floats = (size_t)c.warps_m * (c.rows_per_warp * 2 * nt * 4) * 32;
-    return counters + 2 * (size_t)c.ctas * tile_floats * 4;
+    return partial_region_bytes(sm_count) + counters;
 }
 
 template <int R, int NT>
@@ -608,10 +607,11 @@ int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)
     p.status = device_status_word();
     if (!p.status) return TUNA_ERR_NO_DEVICE;
     const size_t counters = stream_counter_bytes(a.batch * p.row_tiles);
-    if (a.workspace == nullptr || a.workspace_bytes < gemm_stream_workspace_bytes(a.m, a.n, a.k, cfg, a.batch))
+    if (a.workspace == nullptr || a.workspace_bytes < gemm_stream_workspace_bytes(a.m, a.n, a.k, cfg, a.sm_count, a.batch))
         return TUNA_ERR_WORKSPACE;
-    p.counters = (unsigned int *)a.workspace;
-    p.partials = (float *)((uint8_t *)a.workspace + counters);
+    (void)counters;
+    p.partials = (float *)a.workspace;
+    p.counters = (unsigned int *)((uint8_t *)a.workspace + partial_region_bytes(a.sm_count));
     int ctas = cfg.ctas;
     {   // no CTA with less than one block of prefetched steps
         const long long blocks = p.units * (cfg.k_steps / (kLoadsInFlight / cfg.rows_per_warp));
@@ -648,6 +648,17 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[TUNA_NOALLOC_SC
 static __device__ __align__(256) tuna::DeviceStatus g_noalloc_status;
 
 namespace {
+// The array's own compact layout: [counters of this shape][partial tiles of this configuration].
+// The counters are cleared on the stream by every call, so shapes can alternate freely.
+size_t noalloc_scratch_bytes(int m, int k, const tuna_config &c)
+{
+    tuna::StreamParams geo;
+    const int nt = c.tile_tok / 8;
+    tuna::stream_geometry(m, k, c, nt, 1, &geo);
+    const size_t tile_floats = (size_t)c.warps_m * (c.rows_per_warp * 2 * nt * 4) * 32;
+    return tuna::stream_counter_bytes(geo.row_tiles) + 2 * (size_t)c.ctas * tile_floats * 4;
+}
+
 struct NoAllocDevice {
     bool ready = false;
     void *scratch = nullptr;
@@ -692,7 +703,7 @@ extern "C" int tuna_matmul_noalloc(const void *q, const void *x, const void *cod
         st = gemm_stream_normalize_config(m, n, k, sms, &c);
         if (st != TUNA_OK) return st;
     }
-    const size_t need = gemm_stream_workspace_bytes(m, n, k, c);
+    const size_t need = noalloc_scratch_bytes(m, k, c);
     if (need > (size_t)TUNA_NOALLOC_SCRATCH_BYTES) return TUNA_ERR_TOO_LARGE;
     StreamParams geo;
     stream_geometry(m, k, c, c.tile_tok / 8, 1, &geo);

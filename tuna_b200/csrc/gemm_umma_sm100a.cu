@@ -544,8 +544,7 @@ size_t gemm_umma_workspace_bytes(int m, int n, int k, const tuna_config &c, int 
     (void)sm_count;
     const long long tiles = (long long)div_up(m, kBlockRows * c.row_blocks) * div_up(n, c.tile_tok);
     const size_t counters = ((size_t)tiles * 4 + 255) / 256 * 256;
-    const size_t slot = (size_t)c.row_blocks * kBlockRows * c.tile_tok * 4;
-    return counters + 2 * (size_t)c.ctas * slot;
+    return partial_region_bytes(sm_count) + counters;
 }
 
 #ifdef TUNA_PROFILE
@@ -599,8 +598,9 @@ int launch_gemm_umma(const GemmArgs &a, const tuna_config &c)
     cc.ctas = c.ctas;
     if (a.workspace == nullptr || a.workspace_bytes < gemm_umma_workspace_bytes(a.m, a.n, a.k, cc, a.sm_count))
         return TUNA_ERR_WORKSPACE;
-    p.counters = (unsigned int *)a.workspace;
-    p.partials = (float *)((uint8_t *)a.workspace + counters);
+    (void)counters;
+    p.partials = (float *)a.workspace;
+    p.counters = (unsigned int *)((uint8_t *)a.workspace + partial_region_bytes(a.sm_count));
 
     CUtensorMap mq, mx;
     // packed weights as [m/8 row groups][4k bytes]; box = the unit's 16 x row_blocks row groups x 128 bytes (32 columns)

@@ -24,6 +24,15 @@ struct GemmArgs {
     size_t q_stride = 0, x_stride = 0, absmax_stride = 0, o_stride = 0;
 };
 
+// Workspace layout shared by both GEMM kernels: [split-K partial tiles: a region of fixed size]
+// [arrival counters].  The partial region has the same size for every shape and configuration
+// (two slots per CTA, a slot as large as the largest tile either kernel can be configured with),
+// so the counters of any call lie beyond every byte an earlier call may have written partials
+// to: one zero-initialised workspace can be shared by calls of any shapes, the counters being
+// the only part that must be zero and every call leaving them zero.
+constexpr size_t kMaxPartialSlotBytes = 192 * 1024;  // tcgen05 kernel: 128 rows x 384 accumulator columns x 4 bytes
+inline size_t partial_region_bytes(int sm_count) { return 2 * (size_t)sm_count * kMaxPartialSlotBytes; }
+
 struct DeviceStatus;
 // One zero-initialised status word per device; bounded in-kernel waits report into it.
 DeviceStatus *device_status_word();
@@ -38,7 +47,7 @@ cudaError_t launch_dequant(const void *q, const void *absmax, const void *code, 
 
 // mma.sync weight-streaming kernel.  Returns a tuna_status.
 int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg);
-size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &cfg, int batch = 1);
+size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &cfg, int sm_count, int batch = 1);
 int gemm_stream_normalize_config(int m, int n, int k, int sm_count, tuna_config *cfg);
 
 // tcgen05/TMEM kernel.  Returns a tuna_status.

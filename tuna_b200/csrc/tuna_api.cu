@@ -78,7 +78,7 @@ static bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_
 
 static size_t workspace_for(int m, int n, int k, const tuna_config &c, int sm_count)
 {
-    return c.path == TUNA_PATH_STREAM ? gemm_stream_workspace_bytes(m, n, k, c)
+    return c.path == TUNA_PATH_STREAM ? gemm_stream_workspace_bytes(m, n, k, c, sm_count)
                                       : gemm_umma_workspace_bytes(m, n, k, c, sm_count);
 }
 
@@ -130,7 +130,7 @@ extern "C" int tuna_matmul_batched(const void *q, const void *x, const void *cod
     a.stream = (cudaStream_t)stream; a.sm_count = sms;
     if (c.path == TUNA_PATH_STREAM) {
         // one launch over all matrices: the step range of every CTA runs across them
-        const size_t need = gemm_stream_workspace_bytes(m, n, k, c, batch);
+        const size_t need = gemm_stream_workspace_bytes(m, n, k, c, sms, batch);
         if (workspace == nullptr || workspace_bytes < need) return TUNA_ERR_WORKSPACE;
         a.q = (const uint8_t *)q; a.x = x; a.absmax = (const float *)absmax; a.o = o;
         a.batch = batch; a.q_stride = q_stride; a.x_stride = x_stride; a.absmax_stride = absmax_stride; a.o_stride = o_stride;
@@ -156,7 +156,7 @@ extern "C" size_t tuna_matmul_batched_workspace_bytes(int m, int n, int k, int b
     const int sms = device_sm_count();
     tuna_config c;
     if (resolve_config(m, n, k, sms, nullptr, &c) != TUNA_OK) return 0;
-    return c.path == TUNA_PATH_STREAM ? gemm_stream_workspace_bytes(m, n, k, c, batch) : workspace_for(m, n, k, c, sms);
+    return c.path == TUNA_PATH_STREAM ? gemm_stream_workspace_bytes(m, n, k, c, sms, batch) : workspace_for(m, n, k, c, sms);
 }
 
 extern "C" int tuna_matmul(const void *q, const void *x, const void *code, const void *absmax, void *o,

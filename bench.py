@@ -18,7 +18,7 @@ the step); `e2e` calls the op with HOST activations and outputs (pinned memory,
 copies inside the timed region); `roofline` times the dominant kernel alone;
 `cpu_baseline` / `--impl reference` time the CPU restatement of the reference's
 dequantize-then-matmul on the host cores (the reference has no CPU path and no
-CUDA-free build; see DESIGN.md).
+CUDA-free build).
 """
 
 from __future__ import annotations

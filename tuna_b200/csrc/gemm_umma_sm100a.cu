@@ -509,7 +509,7 @@ int gemm_umma_normalize_config(int m, int n, int k, int sm_count, tuna_config *c
     if (t != 16 && t != 32 && t != 64 && t != 128 && t != 256) return TUNA_ERR_BAD_CONFIG;
     if (c->row_blocks == 0) c->row_blocks = (t <= 32) ? 4 : (t <= 64 ? 2 : 1);
     if (c->row_blocks < 1 || c->row_blocks > 4) return TUNA_ERR_BAD_CONFIG;
-    if (c->dequant_warps == 0) c->dequant_warps = 16;
+    if (c->dequant_warps == 0) c->dequant_warps = (t == 256) ? 8 : 16;  // measured on 57344x8192
     if (c->dequant_warps % 4 || c->dequant_warps < 4 || c->dequant_warps > kMaxDequantWarps) return TUNA_ERR_BAD_CONFIG;
     if (c->k_accs == 0) c->k_accs = 1;  // measured: spreading a chunk's MMAs over several accumulators is slower
     if (c->k_accs != 1 && c->k_accs != 2 && c->k_accs != 4) return TUNA_ERR_BAD_CONFIG;

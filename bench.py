@@ -448,8 +448,8 @@ def main():
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of the dominant kernel
 # (profiles/gemm_stream_mistral_mlp_16tok.md), keyed by (m, n, k); None for shapes not captured.
 DRAM_TRAFFIC_PER_LAUNCH: dict = {
-    (28672, 16, 4096): 59.012096e6 + 0.880384e6,
-    (4096, 16, 14336): 29.871872e6,
+    (28672, 16, 4096): 59.009536e6 + 0.886272e6,
+    (4096, 16, 14336): 29.875200e6,
 }
 
 if __name__ == "__main__":

@@ -162,8 +162,7 @@ def load_oracle_lib():
 def run_reference_arm(args, layers, shapes, tokens):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
-        sys.stdout.flush()
-        os._exit(0)  # nothing left to do; skip the interpreter's teardown of CUDA graphs and NCCL state
+        return  # rank 0 alone runs the CPU reference; the other ranks exit 0 without work
     oracle = load_oracle_lib()
     sample_layers = min(layers, 8)
     times, nbytes, threads = cpu_reference_step(shapes, tokens, args.warmup + args.steps, oracle, sample_layers)
@@ -182,9 +181,6 @@ def run_reference_arm(args, layers, shapes, tokens):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
-    if world > 1:
-        sys.stdout.flush()
-        os._exit(0)
 
 
 # --------------------------------------------------------------------------- GPU arm

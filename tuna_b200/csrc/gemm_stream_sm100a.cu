@@ -51,6 +51,11 @@
 // at once (griddepcontrol.launch_dependents) and itself waits for its predecessors
 // (griddepcontrol.wait) only after it has requested its first weights; everything another
 // kernel may have produced (activations, workspace, output) is touched after that wait.
+// Reading the packed weights before the wait is safe even when the preceding kernel of the
+// stream wrote them (a quantizer): a kernel can only start early behind a predecessor that
+// triggers early, the only kernels that do are this one (which never writes weights), and a
+// predecessor that does not trigger has completed - with its writes performed - before a
+// dependent grid starts.
 //
 // The kernel waits on nothing but its own CTA barrier and the stream's kernel order: no
 // spinning on other CTAs, no asynchronous engine.

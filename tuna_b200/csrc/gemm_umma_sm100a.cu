@@ -284,16 +284,17 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
                 const uint32_t xbase = xring + (uint32_t)su * kXStageBytes;
                 const uint32_t dbase = tmem + (uint32_t)dbuf * d_cols;
                 const uint32_t abase = a_base + (uint32_t)(su * J) * kSlotCols;
-                // The unit's J x 4 MMAs go k-step-major over the J row blocks' accumulators
-                // (x k_accs partial accumulators each, summed by the epilogue).
+                // The unit's J x 4 MMAs, row block by row block (x k_accs partial accumulators
+                // each, summed by the epilogue).
+                for (int j = 0; j < J; ++j) {
 #pragma unroll
-                for (int kk = 0; kk < kChunkK / 16; ++kk) {
-                    const uint32_t acc_col = (uint32_t)(kk & (KA - 1)) * N_TILE;
-                    const uint64_t bdesc = make_b_desc(xbase + kk * 32);
-                    const uint32_t fresh = (first && kk < KA) ? 0u : 1u;
-                    for (int j = 0; j < J; ++j)
+                    for (int kk = 0; kk < kChunkK / 16; ++kk) {
+                        const uint32_t acc_col = (uint32_t)(kk & (KA - 1)) * N_TILE;
+                        const uint64_t bdesc = make_b_desc(xbase + kk * 32);
+                        const uint32_t fresh = (first && kk < KA) ? 0u : 1u;
                         tc_mma_ts(dbase + (uint32_t)(j * KA) * N_TILE + acc_col, abase + (uint32_t)j * kSlotCols + kk * 8,
                                   bdesc, idesc, fresh);
+                    }
                 }
                 tc_commit(u_empty + 8 * su);
                 if (last) tc_commit(d_full + 8 * dbuf);

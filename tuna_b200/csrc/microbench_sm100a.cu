@@ -274,23 +274,26 @@ int main()
         run(k_umma<16, 1>, 16, 1, 1);   run(k_umma<64, 1>, 64, 1, 1);   run(k_umma<256, 1>, 256, 1, 1);
     }
     {   // 3, 5
-        const int iters = 20000, warps = 16;
+        const int iters = 20000;
         const size_t smem = 200 * 1024;
-        auto run = [&](auto kern, const char *name) {
+        auto run = [&](auto kern, const char *name, int warps) {
             CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             kern<<<sms, warps * 32, smem>>>(fout, 100);
             CK(cudaDeviceSynchronize());
             cudaEventRecord(e0); kern<<<sms, warps * 32, smem>>>(fout, iters); cudaEventRecord(e1);
             CK(cudaDeviceSynchronize());
             cudaEventElapsedTime(&ms, e0, e1);
-            printf("%s, 16 warps/SM: %.1f weights/clk/SM (HBM needs %.0f)\n", name, (double)sms * warps * iters * 1024 / (ms * 1e-3) / sms / 1.9e9, 6556e9 * 2 / sms / 1.9e9);
+            printf("%s, %d warps/SM: %.1f weights/clk/SM (HBM needs %.0f)\n", name, warps, (double)sms * warps * iters * 1024 / (ms * 1e-3) / sms / 1.9e9, 6556e9 * 2 / sms / 1.9e9);
             return 0;
         };
-        run(k_compute<2, 1>, "[3] table lookups only (prmt + ld.shared, 16 tokens)");
-        run(k_compute<2, 2>, "[5] MMAs only (16 tokens)");
-        run(k_compute<2, 3>, "[5] lookups + MMAs, operands in registers");
-        run(k_compute<2, 7>, "[5] lookups + MMAs + shared-memory operand loads (16 tokens)");
-        run(k_compute<1, 7>, "[5] lookups + MMAs + shared-memory operand loads (8 tokens)");
+        run(k_compute<2, 1>, "[3] table lookups only (prmt + ld.shared, 16 tokens)", 16);
+        run(k_compute<2, 2>, "[5] MMAs only (16 tokens)", 16);
+        run(k_compute<2, 3>, "[5] lookups + MMAs, operands in registers", 16);
+        run(k_compute<2, 7>, "[5] lookups + MMAs + shared-memory operand loads (16 tokens)", 16);
+        run(k_compute<2, 7>, "[5] lookups + MMAs + shared-memory operand loads (16 tokens)", 24);
+        run(k_compute<2, 7>, "[5] lookups + MMAs + shared-memory operand loads (16 tokens)", 32);
+        run(k_compute<1, 7>, "[5] lookups + MMAs + shared-memory operand loads (8 tokens)", 16);
+        run(k_compute<1, 7>, "[5] lookups + MMAs + shared-memory operand loads (8 tokens)", 32);
     }
     {   // 4
         const int kcols = 8192, rows = 57344;

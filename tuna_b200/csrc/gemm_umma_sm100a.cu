@@ -169,7 +169,6 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
     __shared__ __align__(8) uint64_t bars[96];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
-    __shared__ int s_last;
 
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
     const int J = p.row_blocks;
@@ -189,16 +188,13 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
     const uint32_t w_full = bar0, w_empty = w_full + 8 * SW;
     const uint32_t u_full = w_empty + 8 * SW, u_empty = u_full + 8 * SX;
     const uint32_t d_full = u_empty + 8 * SX, d_empty = d_full + 8 * ND;
-    const uint32_t epi_bar = d_empty + 8 * ND;  // the 128 epilogue threads' own barrier
     volatile int *abort_flag = &s_abort;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        s_last = 0;
         for (int i = 0; i < SW; ++i) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, 4 * J); }
         for (int i = 0; i < SX; ++i) { mbar_init(u_full + 8 * i, 1 + 4 * J); mbar_init(u_empty + 8 * i, 1); }
         for (int i = 0; i < ND; ++i) { mbar_init(d_full + 8 * i, 1); mbar_init(d_empty + 8 * i, 4); }
-        mbar_init(epi_bar, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -305,20 +301,11 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
     } else if (warp < kFirstDequantWarp) {
         // ------------------------------------------------------------------ epilogue
         const int quarter = warp & 3;
-        const int et = (warp - kFirstEpilogueWarp) * 32 + lane;  // 0..127 among the epilogue threads
         const int row_in_block = 8 * lane_row_group(quarter, lane) + (lane & 7);
         const int tmem_lane = 32 * quarter + lane;
         UnitCursor c;
         c.init(p, cta, ctas);
         Ring rd;
-        uint32_t epi_phase = 0;
-        // bounded rendezvous of the 128 epilogue threads (a bar.sync could not give up)
-        auto epi_sync = [&]() -> bool {
-            mbar_arrive(epi_bar);
-            const bool r = mbar_wait(epi_bar, epi_phase & 1, abort_flag, p.status, 9);
-            ++epi_phase;
-            return r;
-        };
         while (c.valid()) {
             // the segment: units of one tile inside this CTA's range
             const int tile = c.tile, c0 = c.chunk;
@@ -363,23 +350,27 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
             __syncwarp();
             if (lane == 0) mbar_arrive(d_empty + 8 * dbuf);
             if (!full) {
-                // last arriver at the tile's counter adds every partial in unit order
+                // Each epilogue warp finishes its own 32 rows of the tile's row blocks alone: it
+                // arrives at the counter of (tile, TMEM lane quarter); the last warp to arrive adds
+                // that slice's partials in unit order and stores the rows.  No rendezvous of the
+                // four warps.
                 __threadfence();
-                if (!epi_sync()) break;
+                __syncwarp();
                 const int cta_first = cta_of_unit((long long)tile * p.chunks, p.units, ctas);
                 const int cta_last = cta_of_unit((long long)(tile + 1) * p.chunks - 1, p.units, ctas);
                 const int nseg = cta_last - cta_first + 1;
-                if (et == 0) {
-                    const unsigned int old = atomicAdd(&p.counters[tile], 1u);
-                    const int is_last = (old == (unsigned)nseg - 1);
-                    if (is_last) p.counters[tile] = 0;
-                    s_last = is_last;
-                }
-                if (!epi_sync()) break;
-                const int is_last = s_last;
-                if (!epi_sync()) break;  // s_last may be rewritten by the next segment
-                if (is_last) {
+                unsigned int *counter = p.counters + (size_t)tile * 4 + quarter;
+                unsigned int old = 0;
+                if (lane == 0) old = atomicAdd(counter, 1u);
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == (unsigned)nseg - 1) {
+                    if (lane == 0) *counter = 0;  // leave the counter clean for the next call
                     __threadfence();
+                    auto seg_ptr = [&](int sgm, int j, int piece) {
+                        return reinterpret_cast<const float4 *>(
+                            p.partials + (size_t)(2 * (cta_first + sgm) + (sgm == 0 ? 1 : 0)) * slot_floats +
+                            ((size_t)j * kBlockRows + tmem_lane) * N_TILE + piece * 16);
+                    };
                     for (int j = 0; j < J; ++j) {
                         const int row = (rt * J + j) * kBlockRows + row_in_block;
                         if (row >= p.m) continue;
@@ -389,13 +380,27 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
                             float acc[16];
 #pragma unroll
                             for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-                            for (int s = 0; s < nseg; ++s) {
-                                const float4 *src = reinterpret_cast<const float4 *>(
-                                    p.partials + (size_t)(2 * (cta_first + s) + (s == 0 ? 1 : 0)) * slot_floats +
-                                    ((size_t)j * kBlockRows + tmem_lane) * N_TILE + piece * 16);
+                            // two segments' loads in flight; the adds keep the unit order
+                            int sgm = 0;
+                            for (; sgm + 2 <= nseg; sgm += 2) {
+                                float4 u0[4], u1[4];
+                                const float4 *s0 = seg_ptr(sgm, j, piece), *s1 = seg_ptr(sgm + 1, j, piece);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) { u0[i] = __ldcg(s0 + i); u1[i] = __ldcg(s1 + i); }
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
-                                    const float4 t4 = __ldcg(src + i);
+                                    acc[4 * i] += u0[i].x; acc[4 * i + 1] += u0[i].y; acc[4 * i + 2] += u0[i].z; acc[4 * i + 3] += u0[i].w;
+                                }
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    acc[4 * i] += u1[i].x; acc[4 * i + 1] += u1[i].y; acc[4 * i + 2] += u1[i].z; acc[4 * i + 3] += u1[i].w;
+                                }
+                            }
+                            if (sgm < nseg) {
+                                const float4 *s0 = seg_ptr(sgm, j, piece);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const float4 t4 = __ldcg(s0 + i);
                                     acc[4 * i] += t4.x; acc[4 * i + 1] += t4.y; acc[4 * i + 2] += t4.z; acc[4 * i + 3] += t4.w;
                                 }
                             }
@@ -544,7 +549,7 @@ size_t gemm_umma_workspace_bytes(int m, int n, int k, const tuna_config &c, int 
 {
     (void)sm_count;
     const long long tiles = (long long)div_up(m, kBlockRows * c.row_blocks) * div_up(n, c.tile_tok);
-    const size_t counters = ((size_t)tiles * 4 + 255) / 256 * 256;
+    const size_t counters = ((size_t)tiles * 16 + 255) / 256 * 256;  // one counter per tile and TMEM lane quarter
     return partial_region_bytes(sm_count) + counters;
 }
 
@@ -592,7 +597,7 @@ int launch_gemm_umma(const GemmArgs &a, const tuna_config &c)
     p.status = device_status_word();
     if (!p.status) return TUNA_ERR_NO_DEVICE;
     const long long tiles = (long long)p.row_tiles * p.tok_tiles;
-    const size_t counters = ((size_t)tiles * 4 + 255) / 256 * 256;
+    const size_t counters = ((size_t)tiles * 16 + 255) / 256 * 256;  // one counter per tile and TMEM lane quarter
     int ctas = c.ctas;
     if ((long long)ctas > p.units) ctas = (int)p.units;
     tuna_config cc = c;

@@ -217,7 +217,6 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
     const uint32_t d_cols = (uint32_t)J * KA * N_TILE;     // columns of one accumulator buffer
     const uint32_t a_base = tmem + (uint32_t)ND * d_cols;  // first A-operand slot
 
-    PROF_ROLE_BEGIN();
     if (warp == 0) {
         // ------------------------------------------------------------------ weight producer
         // The whole warp runs the loop and the waits; one elected lane issues the copies.  A
@@ -473,7 +472,6 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
     }
 
     // ------------------------------------------------------------------ common exit
-    PROF_ROLE_END(warp < kFirstDequantWarp ? warp : kFirstDequantWarp);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -553,17 +551,6 @@ size_t gemm_umma_workspace_bytes(int m, int n, int k, const tuna_config &c, int 
     return partial_region_bytes(sm_count) + counters;
 }
 
-#ifdef TUNA_PROFILE
-extern "C" void tunadbg_prof(long long *out, int reset)
-{
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 32);
-    if (reset) {
-        long long z[32] = {0};
-        cudaMemcpyToSymbol(g_prof, z, sizeof(z));
-    }
-}
-#endif
 
 template <int N_TILE>
 static int launch_umma(const UmmaParams &p, const CUtensorMap &mq, const CUtensorMap &mx, int ctas, int threads,

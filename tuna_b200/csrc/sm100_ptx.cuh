@@ -47,18 +47,6 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
         }
     }
 }
-#ifdef TUNA_PROFILE
-// Debug build only: cycles CTA 0 spends in each wait site ([where]) and in each role ([16 + role]).
-__device__ long long g_prof[32];
-#define PROF_ROLE_BEGIN() const long long _role_t0 = clock64()
-#define PROF_ROLE_END(role)                                                            \
-    do {                                                                               \
-        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_prof[16 + (role)] = clock64() - _role_t0; \
-    } while (0)
-#else
-#define PROF_ROLE_BEGIN()
-#define PROF_ROLE_END(role)
-#endif
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                           DeviceStatus *status, int where)

@@ -262,11 +262,31 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
         // issued an MMA every 130-290 clocks; the converged warp needs about 43.)  The tensor
         // pipe queues hardly more than one MMA behind the running one, so everything this
         // loop does besides issuing is kept short: one wait and one commit per unit.
+        // When the following unit of the same segment is already complete as well, both are issued
+        // in one trip: one round of loop bookkeeping and waiting for eight MMAs instead of four.
         UnitCursor c;
         c.init(p, cta, ctas);
         constexpr uint32_t idesc = make_idesc(N_TILE);
         Ring ru, rd;
-        for (; c.valid(); c.next(p), ru.advance(SX)) {
+        // the unit's J x 4 MMAs, row block by row block (x k_accs partial accumulators each,
+        // summed by the epilogue), then the commit that releases its stage
+        auto issue_unit = [&](const int su, const int dbuf, const bool first) {
+            const uint32_t xbase = xring + (uint32_t)su * kXStageBytes;
+            const uint32_t dbase = tmem + (uint32_t)dbuf * d_cols;
+            const uint32_t abase = a_base + (uint32_t)(su * J) * kSlotCols;
+            for (int j = 0; j < J; ++j) {
+#pragma unroll
+                for (int kk = 0; kk < kChunkK / 16; ++kk) {
+                    const uint32_t acc_col = (uint32_t)(kk & (KA - 1)) * N_TILE;
+                    const uint64_t bdesc = make_b_desc(xbase + kk * 32);
+                    const uint32_t fresh = (first && kk < KA) ? 0u : 1u;
+                    tc_mma_ts(dbase + (uint32_t)(j * KA) * N_TILE + acc_col, abase + (uint32_t)j * kSlotCols + kk * 8, bdesc,
+                              idesc, fresh);
+                }
+            }
+            tc_commit(u_empty + 8 * su);
+        };
+        while (c.valid()) {
             const bool first = c.first_of_segment();
             const bool last = (c.left == 1) || (c.chunk + 1 == p.chunks);
             const int dbuf = rd.idx, su = ru.idx;
@@ -274,28 +294,26 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
             if (first) ok = mbar_wait(d_empty + 8 * dbuf, rd.phase ^ 1, abort_flag, p.status, 3);
             ok = ok && mbar_wait(u_full + 8 * su, ru.phase, abort_flag, p.status, 4);
             if (!__all_sync(0xffffffffu, ok)) break;
+            // the next unit, if it belongs to the same segment and has landed already
+            Ring ru2 = ru;
+            ru2.advance(SX);
+            bool pair = !last && mbar_try_wait(u_full + 8 * ru2.idx, ru2.phase);
+            pair = __all_sync(0xffffffffu, pair) != 0;
+            const bool last2 = pair && ((c.left == 2) || (c.chunk + 2 == p.chunks));
             tc_fence_after();
             if (elect_one_sync()) {
-                const uint32_t xbase = xring + (uint32_t)su * kXStageBytes;
-                const uint32_t dbase = tmem + (uint32_t)dbuf * d_cols;
-                const uint32_t abase = a_base + (uint32_t)(su * J) * kSlotCols;
-                // The unit's J x 4 MMAs, row block by row block (x k_accs partial accumulators
-                // each, summed by the epilogue).
-                for (int j = 0; j < J; ++j) {
-#pragma unroll
-                    for (int kk = 0; kk < kChunkK / 16; ++kk) {
-                        const uint32_t acc_col = (uint32_t)(kk & (KA - 1)) * N_TILE;
-                        const uint64_t bdesc = make_b_desc(xbase + kk * 32);
-                        const uint32_t fresh = (first && kk < KA) ? 0u : 1u;
-                        tc_mma_ts(dbase + (uint32_t)(j * KA) * N_TILE + acc_col, abase + (uint32_t)j * kSlotCols + kk * 8,
-                                  bdesc, idesc, fresh);
-                    }
-                }
-                tc_commit(u_empty + 8 * su);
-                if (last) tc_commit(d_full + 8 * dbuf);
+                issue_unit(su, dbuf, first);
+                if (pair) issue_unit(ru2.idx, dbuf, false);
+                if (last || last2) tc_commit(d_full + 8 * dbuf);
             }
             __syncwarp();
-            if (last) rd.advance(ND);
+            c.next(p);
+            ru.advance(SX);
+            if (pair) {
+                c.next(p);
+                ru.advance(SX);
+            }
+            if (last || last2) rd.advance(ND);
         }
     } else if (warp < kFirstDequantWarp) {
         // ------------------------------------------------------------------ epilogue

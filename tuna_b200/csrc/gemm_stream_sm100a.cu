@@ -139,7 +139,9 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr)
     return v;
 }
 
-template <int R, int NT>
+// BATCHED: the tile index runs over several matrices (tuna_matmul_batched); without it the
+// matrix index is the constant 0 and its bookkeeping compiles away.
+template <int R, int NT, bool BATCHED>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const StreamParams p)
 {
     constexpr int PF = kLoadsInFlight / R;  // steps of weights in flight per warp
@@ -176,7 +178,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
         return gstep < big ? gstep / (p.steps_q + 1) : p.steps_r + (gstep - big) / p.steps_q;
     };
     int tile = g_begin / tile_steps;  // over all matrices of the batch
-    int tile_b = tile / p.row_tiles, tile_rt = tile - tile_b * p.row_tiles;  // matrix, row tile inside it
+    int tile_b = BATCHED ? tile / p.row_tiles : 0;  // matrix, row tile inside it
+    int tile_rt = tile - tile_b * p.row_tiles;
     const int first_in_tile = g_begin - tile * tile_steps;
     int chunk = first_in_tile / S;
     // positions below are relative to the first step of the first unit this CTA touches
@@ -237,7 +240,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
             ps0 = 0;
             if (++pchunk == p.chunks) {
                 pchunk = 0;
-                if (++prt == p.row_tiles) { prt = 0; ++pb; }
+                ++prt;
+                if (BATCHED && prt == p.row_tiles) { prt = 0; ++pb; }
             }
         }
     };
@@ -437,7 +441,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
         const bool last_unit = pos + S >= r_end;
         if (!last_unit) {  // next unit, other buffer
             const bool wrap = chunk + 1 == p.chunks;
-            stage_x((wrap && tile_rt + 1 == p.row_tiles) ? tile_b + 1 : tile_b, wrap ? 0 : chunk + 1, xb ^ 1);
+            stage_x((BATCHED && wrap && tile_rt + 1 == p.row_tiles) ? tile_b + 1 : tile_b, wrap ? 0 : chunk + 1, xb ^ 1);
         }
         if (active) {
             const int s_first = (s_lo / PF) * PF;
@@ -473,7 +477,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
         if (++chunk == p.chunks) {
             chunk = 0;
             ++tile;
-            if (++tile_rt == p.row_tiles) { tile_rt = 0; ++tile_b; }
+            ++tile_rt;
+            if (BATCHED && tile_rt == p.row_tiles) { tile_rt = 0; ++tile_b; }
         }
         if (seg_end) seg_t0 = 0;  // a later segment of this CTA starts a tile
     }
@@ -572,14 +577,14 @@ size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &c, in
     return partial_region_bytes(sm_count) + counters;
 }
 
-template <int R, int NT>
-static int launch_one(const StreamParams &p, int ctas, size_t smem, cudaStream_t stream)
+template <int R, int NT, bool BATCHED>
+static int launch_one_b(const StreamParams &p, int ctas, size_t smem, cudaStream_t stream)
 {
     static bool attr_set[64] = {false};  // one-time, per device, opt-in to large dynamic shared memory
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TUNA_ERR_NO_DEVICE;
     if (!attr_set[dev]) {
-        if (cudaFuncSetAttribute(gemm_stream_kernel<R, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemm_stream_kernel<R, NT, BATCHED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kStreamSmemLimit) != cudaSuccess)
             return TUNA_ERR_NO_DEVICE;
         attr_set[dev] = true;
@@ -596,7 +601,13 @@ static int launch_one(const StreamParams &p, int ctas, size_t smem, cudaStream_t
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    return cudaLaunchKernelEx(&lc, gemm_stream_kernel<R, NT>, p) == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
+    return cudaLaunchKernelEx(&lc, gemm_stream_kernel<R, NT, BATCHED>, p) == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
+}
+
+template <int R, int NT>
+static int launch_one(const StreamParams &p, int ctas, size_t smem, cudaStream_t stream)
+{
+    return p.batch > 1 ? launch_one_b<R, NT, true>(p, ctas, smem, stream) : launch_one_b<R, NT, false>(p, ctas, smem, stream);
 }
 
 int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)

@@ -11,7 +11,9 @@ Parity status: the reference ships no golden vectors and no asserting tests
 two other ways: (1) against fixtures under ``tests/golden/`` that were produced
 by the reference's own CUDA kernels compiled from its sources and run on a
 B200 (see ``tests/golden/make_reference_fixtures.py``), and (2) against a
-second, independent restatement in C (``oracle/tuna_oracle.c``).
+second, independent restatement in C (``oracle/tuna_oracle.c``).  The quantizer
+is pinned by the reference's torch expression evaluated on the CPU
+(``tests/golden/make_quantizer_fixture.py``).
 
 Naming follows the reference: ``m`` = output features (rows of W), ``n`` =
 tokens, ``k`` = reduction length; ``x`` is ``[n, k]``, ``W`` is ``[m, k]`` and

@@ -5,13 +5,12 @@
 // mma orientation (weights are the m16 "A" operand, tokens the n8 "B" operand,
 // kernel.cu:2182-2192) and nothing else.
 //
-// Why mma.sync here and not tcgen05: measured on B200, one tcgen05.mma (M=128, K=16, A from
-// tensor memory) costs its issuing warp at least ~43 clocks whatever N is.  With the weights as
-// the M=128 operand and 16 tokens as N that is 2048 weights per 43 clocks = 47 per clock per SM
-// with nothing else in the issuing warp's loop (27 with a pipeline's waits and commits), no
-// better than what HBM delivers (47 per clock per SM); mma.sync.m16n8k16 on 16 warps sustains
-// 45.6 weights per clock at 16 tokens without a single serial issuer.  The tensor-memory
-// kernel takes over for large token counts.
+// Why mma.sync here: measured on B200, mma.sync.m16n8k16 on 16 warps sustains 45.6 weights per
+// clock per SM at 16 tokens with no serial issuer and no cross-role synchronisation, against the
+// 47 that HBM delivers.  The tensor pipe is far faster through tcgen05 (a 128x16x16 MMA takes
+// 11.6 clocks from a tight issuing loop), but each wait, commit or stray instruction of the
+// issuing warp shows up directly and the tensor-memory kernel's dequant pipeline is not yet
+// fast enough at small token tiles; it takes over for large token counts.
 //
 // Data movement, also chosen by measurement on B200 in this kernel's access pattern (a warp
 // load = four 128-byte runs, one per row group): 128-bit ld.global straight into a register

@@ -259,7 +259,8 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
         // ------------------------------------------------------------------ MMA issue
         // The warp stays converged: every lane executes the loop and the waits, one elected
         // lane issues the MMAs and commits.  (A single diverged thread running this loop
-        // issued an MMA every 130-290 clocks; the converged warp needs about 43.)  The tensor
+        // issued an MMA every 130-290 clocks; from a converged warp with a tight loop the pipe runs
+        // at its ideal rate, 11.6 clocks at N = 16 up to 128 at N = 256.)  The tensor
         // pipe queues hardly more than one MMA behind the running one, so everything this
         // loop does besides issuing is kept short: one wait and one commit per unit.
         // When the following unit of the same segment is already complete as well, both are issued

@@ -51,8 +51,9 @@ __global__ void k_mma_sync(float *out, int iters)
     if (s == 123.456f) out[0] = s;
 }
 
-// ---- 2. tcgen05.mma cost: warp 1, converged, issues `iters` MMAs (elect.sync picks the lane) into one
-// accumulator, four per loop trip with compile-time operand offsets, then commits.  `per_group` adds what a
+// ---- 2. tcgen05.mma cost: warp 1, converged, issues `iters` MMAs (elect.sync picks the lane), four per
+// loop trip with compile-time operand offsets, then commits.  `accumulators` = 1: every MMA accumulates
+// into the same tile (a dependent chain); 2: consecutive groups of four alternate between two tiles.  PER_GROUP adds what a
 // pipeline stage costs the issuing warp: two waits on barriers that are already complete and two commits.
 static __device__ __forceinline__ uint32_t elect_one()
 {
@@ -64,8 +65,8 @@ static __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-template <int N_TILE, int A_FROM_TMEM>
-__global__ void __launch_bounds__(256, 1) k_umma(int groups, int per_group, long long *out, int *err)
+template <int N_TILE, int A_FROM_TMEM, int PER_GROUP>
+__global__ void __launch_bounds__(256, 1) k_umma(int groups, int accumulators, long long *out, int *err)
 {
     extern __shared__ __align__(1024) uint8_t sm[];
     __shared__ __align__(8) uint64_t bar, bar_stage, bar_ready;
@@ -93,7 +94,8 @@ __global__ void __launch_bounds__(256, 1) k_umma(int groups, int per_group, long
         const long long t0 = clock64();
         for (int g = 0; g < groups; ++g) {
             const uint32_t a_t = tm + 256 + (g & 7) * 32, b_s = sbase + (g & 3) * 32768, a_s = sbase + 131072 + (g & 1) * 16384;
-            if (per_group) {
+            const uint32_t d_t = tm + (uint32_t)(g & (accumulators - 1)) * N_TILE;  // consecutive groups on different accumulators (power of two)
+            if (PER_GROUP) {
                 for (int w = 0; w < 2; ++w) {
                     uint32_t ok = 0;  // parity 1 of a fresh barrier: the wait returns at once
                     while (!ok) asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 1; selp.u32 %0,1,0,p; }" : "=r"(ok) : "r"(s32(&bar_ready)) : "memory");
@@ -103,13 +105,13 @@ __global__ void __launch_bounds__(256, 1) k_umma(int groups, int per_group, long
             if (elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
-                    const uint32_t acc = (g | kk) != 0;
+                    const uint32_t acc = (g >= accumulators || kk != 0);
                     if (A_FROM_TMEM)
-                        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(tm), "r"(a_t + kk * 8), "l"(desc(b_s + kk * 32)), "r"(idesc), "r"(acc) : "memory");
+                        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(d_t), "r"(a_t + kk * 8), "l"(desc(b_s + kk * 32)), "r"(idesc), "r"(acc) : "memory");
                     else
-                        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tm), "l"(desc(a_s + kk * 32)), "l"(desc(b_s + kk * 32)), "r"(idesc), "r"(acc) : "memory");
+                        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_t), "l"(desc(a_s + kk * 32)), "l"(desc(b_s + kk * 32)), "r"(idesc), "r"(acc) : "memory");
                 }
-                if (per_group) { umma_commit(s32(&bar_stage)); umma_commit(s32(&bar_stage)); }
+                if (PER_GROUP) { umma_commit(s32(&bar_stage)); umma_commit(s32(&bar_stage)); }
             }
             __syncwarp();
         }
@@ -255,23 +257,26 @@ int main()
         printf("[1] mma.sync m16n8k16 f16->f32, 16 warps/SM: %.0f TFLOP/s, %.0f MAC/clk/SM\n", 2 * macs / ms / 1e9, macs / (ms * 1e-3) / sms / 1.9e9);
     }
     {   // 2
-        auto run = [&](auto kern, int n, int a_tmem, int per_group) {
+        auto run = [&](auto kern, int n, int a_tmem, int per_group, int accs) {
             CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 170 * 1024));
             const int groups = 1000;
-            kern<<<sms, 256, 170 * 1024>>>(groups, per_group, lout, derr);
+            kern<<<sms, 256, 170 * 1024>>>(groups, accs, lout, derr);
             CK(cudaDeviceSynchronize());
             long long h;
             int he;
             cudaMemcpy(&h, lout, 8, cudaMemcpyDeviceToHost);
             cudaMemcpy(&he, derr, 4, cudaMemcpyDeviceToHost);
-            printf("[2] tcgen05.mma kind::f16 M=128 N=%3d K=16, A from %s%s: %.1f clk per MMA (ideal %d; timeout flag %d)\n", n,
-                   a_tmem ? "TMEM" : "smem", per_group ? ", +2 waits +2 commits per 4 MMAs" : "", (double)h / (groups * 4), n / 2, he);
+            printf("[2] tcgen05.mma kind::f16 M=128 N=%3d K=16, A from %s, %d accumulator%s%s: %.1f clk per MMA (ideal %d; timeout flag %d)\n", n,
+                   a_tmem ? "TMEM" : "smem", accs, accs > 1 ? "s" : "", per_group ? ", +2 waits +2 commits per 4 MMAs" : "",
+                   (double)h / (groups * 4), n / 2, he);
             return 0;
         };
-        run(k_umma<16, 1>, 16, 1, 0);   run(k_umma<32, 1>, 32, 1, 0);   run(k_umma<64, 1>, 64, 1, 0);
-        run(k_umma<128, 1>, 128, 1, 0); run(k_umma<256, 1>, 256, 1, 0);
-        run(k_umma<16, 0>, 16, 0, 0);   run(k_umma<64, 0>, 64, 0, 0);   run(k_umma<256, 0>, 256, 0, 0);
-        run(k_umma<16, 1>, 16, 1, 1);   run(k_umma<64, 1>, 64, 1, 1);   run(k_umma<256, 1>, 256, 1, 1);
+        run(k_umma<16, 1, 0>, 16, 1, 0, 1);   run(k_umma<32, 1, 0>, 32, 1, 0, 1);   run(k_umma<64, 1, 0>, 64, 1, 0, 1);
+        run(k_umma<128, 1, 0>, 128, 1, 0, 1); run(k_umma<256, 1, 0>, 256, 1, 0, 1);
+        run(k_umma<16, 1, 0>, 16, 1, 0, 2);   run(k_umma<32, 1, 0>, 32, 1, 0, 2);   run(k_umma<64, 1, 0>, 64, 1, 0, 2);
+        run(k_umma<16, 0, 0>, 16, 0, 0, 1);   run(k_umma<64, 0, 0>, 64, 0, 0, 1);   run(k_umma<256, 0, 0>, 256, 0, 0, 1);
+        run(k_umma<16, 1, 1>, 16, 1, 1, 1);   run(k_umma<64, 1, 1>, 64, 1, 1, 1);   run(k_umma<256, 1, 1>, 256, 1, 1, 1);
+        run(k_umma<16, 1, 1>, 16, 1, 1, 2);   run(k_umma<64, 1, 1>, 64, 1, 1, 2);
     }
     {   // 3, 5
         const int iters = 20000;

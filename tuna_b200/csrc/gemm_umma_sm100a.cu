@@ -451,42 +451,51 @@ gemm_w4a16_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap t
             off[kt] = (uint32_t)rg * 128 + ((uint32_t)((2 * kt + (r >> 2)) ^ (rg & 7)) << 4) + (uint32_t)(r & 3) * 4;
         const uint32_t *lut_lane = lut + lane;
         const uint32_t half_bytes = (uint32_t)J * 2048;  // one column half of a weight stage
+        // Tasks (unit, row block j) are numbered unit-major; group g takes the tasks g, g + G, ...
+        // and walks only those: its position is (unit, j) plus the two ring positions of `unit`.
         UnitCursor c;
         c.init(p, cta, ctas);
+        const int total = c.total;
+        auto ring_skip = [](Ring &r, int n, int depth) {
+            r.idx += n;
+            while (r.idx >= depth) { r.idx -= depth; r.phase ^= 1u; }
+        };
         Ring rw, ru;
-        int turn = 0;  // task index modulo the number of dequant groups
-        bool ok = true;
-        for (; ok && c.valid(); c.next(p), rw.advance(SW), ru.advance(SX)) {
+        int unit = 0, j = group;
+        while (j >= J) { j -= J; ++unit; }
+        ring_skip(rw, unit, SW);
+        ring_skip(ru, unit, SX);
+        while (unit < total) {
             const int sw = rw.idx, su = ru.idx;
-            bool waited = false;
-            for (int j = 0; j < J; ++j, turn = (turn + 1 == G) ? 0 : turn + 1) {
-                if (turn != group) continue;
-                if (!waited) {
-                    if (!mbar_wait(w_full + 8 * sw, rw.phase, abort_flag, p.status, 7)) { ok = false; break; }
-                    waited = true;
-                }
-                const int slot = su * J + j;
-                const uint32_t wb = wring + (uint32_t)(sw * J) * kWBlockBytes + (uint32_t)j * 2048;
-                uint32_t w[8];
+            if (!mbar_wait(w_full + 8 * sw, rw.phase, abort_flag, p.status, 7)) break;
+            const int slot = su * J + j;
+            const uint32_t wb = wring + (uint32_t)(sw * J) * kWBlockBytes + (uint32_t)j * 2048;
+            uint32_t w[8];
 #pragma unroll
-                for (int kt = 0; kt < 8; ++kt)
-                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[kt]) : "r"(wb + (uint32_t)(kt >> 2) * half_bytes + off[kt & 3]));
-                uint32_t v[32];
+            for (int kt = 0; kt < 8; ++kt)
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[kt]) : "r"(wb + (uint32_t)(kt >> 2) * half_bytes + off[kt & 3]));
+            uint32_t v[32];
 #pragma unroll
-                for (int kt = 0; kt < 8; ++kt)
+            for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
-                    for (int b = 0; b < 4; ++b) v[kt * 4 + b] = lut_lane[((w[kt] >> (8 * b)) & 0xffu) * 32];
-                if (!mbar_wait(u_empty + 8 * su, ru.phase ^ 1, abort_flag, p.status, 8)) { ok = false; break; }
-                tc_fence_after();
-                tc_st_x32(a_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)slot * kSlotCols, v);
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(u_full + 8 * su);
-                    mbar_arrive(w_empty + 8 * sw);
-                }
+                for (int b = 0; b < 4; ++b) v[kt * 4 + b] = lut_lane[((w[kt] >> (8 * b)) & 0xffu) * 32];
+            if (!mbar_wait(u_empty + 8 * su, ru.phase ^ 1, abort_flag, p.status, 8)) break;
+            tc_fence_after();
+            tc_st_x32(a_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)slot * kSlotCols, v);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(u_full + 8 * su);
+                mbar_arrive(w_empty + 8 * sw);
             }
+            // the group's next task
+            j += G;
+            int skip = 0;
+            while (j >= J) { j -= J; ++skip; }
+            unit += skip;
+            ring_skip(rw, skip, SW);
+            ring_skip(ru, skip, SX);
         }
     }
 

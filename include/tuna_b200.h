@@ -46,7 +46,9 @@ typedef enum tuna_status {
 typedef enum tuna_path {
     TUNA_PATH_AUTO = 0,
     TUNA_PATH_STREAM = 1, /* register-streaming mma.sync kernel, small token counts       */
-    TUNA_PATH_UMMA = 2    /* tcgen05/TMEM kernel: TMA-staged, dequant into TMEM       */
+    TUNA_PATH_UMMA = 2,   /* tcgen05/TMEM kernel: TMA-staged, dequant into TMEM       */
+    TUNA_PATH_TSTREAM = 3 /* tcgen05 weight-streaming kernel: ld.global -> table ->   *
+                           * tcgen05.st fragments, small token counts                 */
 } tuna_path;
 
 /* Launch configuration, the Blackwell counterpart of the reference's
@@ -54,7 +56,8 @@ typedef enum tuna_path {
  * param_map.json, or filled by hand (tuner, tests).  Zero means "default". */
 typedef struct tuna_config {
     int32_t path;          /* tuna_path                                               */
-    int32_t tile_tok;      /* tokens per pass: stream 8|16|32; umma 16|32|64|128|256  */
+    int32_t tile_tok;      /* tokens per pass: stream 8|16|32; tstream 16|32|64;      *
+                            * umma 16|32|64|128|256                                   */
     int32_t rows_per_warp; /* stream: 32-row blocks per warp (1|2)                    */
     int32_t warps_m;       /* stream: consumer warps along output rows (power of 2)   */
     int32_t warps_k;       /* stream: consumer warps along K (power of 2, m*k <= 16)  */
@@ -63,7 +66,7 @@ typedef struct tuna_config {
     int32_t stages_w;      /* umma: packed-weight ring depth (64-column stages)       */
     int32_t stages_x;      /* umma: unit stages (activation tile + A-operand slots)   */
     int32_t dequant_warps; /* umma: warps converting codes into TMEM (mult of 4)      */
-    int32_t row_blocks;    /* umma: 128-row blocks per CTA tile (1|2|4)               */
+    int32_t row_blocks;    /* umma, tstream: 128-row blocks per CTA tile (1|2|4)      */
     int32_t stages_a;      /* umma: derived (stages_x * row_blocks TMEM operand slots) */
     int32_t k_accs;        /* umma: accumulators per row block along K (1|2|4)        */
     int32_t reserved[3];
@@ -84,7 +87,8 @@ typedef struct tuna_config {
  * the partial-sum region, so ONE zero-initialised allocation (sized for the
  * largest shape) serves consecutive calls of any shapes on one stream; calls
  * that overlap on the device need separate workspaces.  Alignment: q, x, o,
- * workspace 16 bytes; absmax, code 4 bytes.
+ * workspace 16 bytes; absmax, code 4 bytes (absmax may be a slice of a larger
+ * scale buffer).
  */
 int tuna_matmul(const void *q, const void *x, const void *code, const void *absmax, void *o,
                 int m, int n, int k, void *workspace, size_t workspace_bytes, void *stream);
@@ -128,10 +132,11 @@ int tuna_check_device_status(void *stream);
  * arrays of the library, TUNA_NOALLOC_SCRATCH_BYTES in total, which every GPU that loads the
  * library keeps until the process exits.  It never calls cudaMalloc, cudaFree or an allocating
  * library routine.
- *  - Same arguments, layouts and result as tuna_matmul (small-token-count kernel, any n; more than
+ *  - Same arguments, layouts and result as tuna_matmul (mma.sync streaming kernel, any n; more than
  *    32 tokens run as several passes).  A shape whose scratch would exceed the array returns
- *    TUNA_ERR_TOO_LARGE; with one CTA per SM on a 148-SM part the partial tiles need at most
- *    19.4 MB, so in practice only the tile counters of matrices beyond ~10^8 rows do not fit.
+ *    TUNA_ERR_TOO_LARGE.  The scratch is 64 bytes of counters per row tile (a row tile is 32 to
+ *    1024 rows, chosen with the configuration) plus two partial tiles per CTA, at most 18.5 MiB
+ *    on a 148-SM part; with the largest partial tiles about 24 000 row tiles still fit.
  *  - The first call on a device looks up the arrays' device addresses (cudaGetSymbolAddress) and
  *    opts the kernel into large shared memory; make that first call outside any stream capture.
  *  - All calls share the one array per device and it keeps the previous call's contents (the part
@@ -182,9 +187,12 @@ int tuna_last_wrapper_status(void);
  * The reference's own two native entry points, with their C++ linkage and parameter lists
  * (declared in extension.cpp:22-24, defined in kernel.cu:3009 and kernel.cu:3243), so that the
  * reference's pybind module links against this library unchanged.  `wrapper` takes its scratch
- * from a per-device allocation cached inside the library (grown on demand, zero-filled once);
- * neither function reports errors (the reference's do not either): read
- * tuna_last_wrapper_status() after the call.
+ * from an allocation cached inside the library per (device, stream), so calls on different
+ * streams may overlap as they may in the reference.  The first call on a stream (and a call
+ * that needs a larger scratch than any before it) allocates: make it outside stream capture -
+ * during capture such a call fails with TUNA_ERR_WORKSPACE.  Buffers are never freed while the
+ * process lives (a captured graph may refer to them).  Neither function reports errors (the
+ * reference's do not either): read tuna_last_wrapper_status() after the call.
  */
 struct CUstream_st;
 void wrapper(void *q, void *x, void *c, void *s, void *o, int m, int n, int k, CUstream_st *stream);

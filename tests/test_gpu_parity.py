@@ -122,12 +122,13 @@ def test_matmul_is_deterministic_and_needs_no_zero_fill(m, k, n):
             first = got
         else:
             assert np.array_equal(first, got), f"run {it} differs"
-    # the workspace is left clean: only partial sums may remain, counters are zero again
-    cfg = _lib.TunaConfig()
-    _lib.load().tuna_lookup_config(m, n, k, ctypes.byref(cfg))
-    if cfg.path == _lib.PATH_STREAM:
-        tiles = -(-m // (32 * cfg.rows_per_warp * cfg.warps_m))
-        assert int(ws[: tiles * 4].view(torch.int32).abs().sum()) == 0
+    # the workspace is left clean: only partial sums may remain; the arrival counters, which live
+    # behind the partial region (2 slots x SMs x 192 KB), are zero again
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    counters_at = 2 * sms * 192 * 1024
+    need = int(_lib.load().tuna_matmul_workspace_bytes(m, n, k))
+    assert need > counters_at
+    assert int(ws[counters_at:need].view(torch.int32).abs().sum()) == 0
     assert _lib.load().tuna_check_device_status(stream_ptr()) == 0
 
 
@@ -259,3 +260,95 @@ def test_one_workspace_serves_alternating_shapes_and_kernels():
             assert st == 0
             check_parity(out.cpu().numpy(), orc.matmul_ref(*host, m, n, k), TOL)
             assert holder.guards_intact()
+
+
+def _sampled_rows_check(m, n, k, seed, code=None, cfg=None):
+    """Full-size shapes: the oracle runs on a random sample of 8-row groups (plus first and last)."""
+    (x, q, absmax, nf4), dev = make_case(m, n, k, seed=seed)
+    if code is not None:
+        dev[3] = torch.from_numpy(code).cuda()
+    else:
+        code = nf4
+    st, out, holder = run_matmul(dev, m, n, k, cfg=cfg)
+    assert st == 0, _lib.load().tuna_status_string(st)
+    assert _lib.load().tuna_check_device_status(stream_ptr()) == 0, "a bounded wait ran out"
+    rng = np.random.default_rng(seed)
+    rows = np.unique(np.concatenate([rng.integers(0, m // 8, 24), [0, m // 8 - 1]]))
+    q3 = q.reshape(m // 8, k // 8, 32)
+    ref = orc.matmul_ref(x, q3[rows], absmax.reshape(-1, 8)[rows].ravel(), code, len(rows) * 8, n, k)
+    got = out.cpu().numpy().reshape(n, m // 8, 8)[:, rows].reshape(n, -1)
+    check_parity(got, ref, TOL)
+    assert holder.guards_intact()
+
+
+# BASELINE config 4: the token sweep on the Llama-70B gate+up shape, default dispatch
+# (reference buckets kernel.cu:3034, 3049, 3079, 3109, 3139, 3154)
+@pytest.mark.parametrize("n", [1, 64, 256, 1024, 2048])
+def test_matmul_llama70b_gateup_token_sweep(n):
+    _sampled_rows_check(57344, n, 8192, seed=400 + n)
+
+
+# the token counts a survey of the reference's buckets suggests, at a full benchmark size
+@pytest.mark.parametrize("n", [7, 8, 17, 64, 100, 128])
+def test_matmul_mistral_gateup_token_counts(n):
+    _sampled_rows_check(28672, n, 4096, seed=500 + n)
+
+
+# BASELINE config 3: the Mixtral combined-expert shapes
+@pytest.mark.parametrize("m,k", [(229376, 4096), (32768, 14336)])
+def test_matmul_mixtral_combined_shapes_m16(m, k):
+    _sampled_rows_check(m, 16, k, seed=m + k)
+
+
+# the per-GPU shards of configs 1 and 2 at 2, 4 and 8 GPUs (column-parallel: rows / g; row-parallel: k / g)
+SHARD_SHAPES = [
+    (14336, 4096), (7168, 4096), (3584, 4096), (4096, 7168), (4096, 3584), (4096, 1792),
+    (28672, 8192), (7168, 8192), (8192, 14336), (8192, 3584), (5120, 8192), (1280, 8192), (8192, 4096), (8192, 1024),
+]
+
+
+@pytest.mark.parametrize("m,k", SHARD_SHAPES)
+def test_matmul_shard_shapes_m16(m, k):
+    _sampled_rows_check(m, 16, k, seed=m * 3 + k)
+
+
+@pytest.mark.parametrize("m,n,k", [(4096, 16, 4096), (1024, 64, 2048), (520, 5, 264)])
+def test_matmul_arbitrary_codebook(m, n, k):
+    """The codebook is a run-time argument (test.py:19-40 passes NF4; any 16 values must work)."""
+    code = np.random.default_rng(77).standard_normal(16).astype(np.float32)
+    _sampled_rows_check(m, n, k, seed=m + n, code=code)
+
+
+def test_matmul_absmax_only_4_byte_aligned():
+    """absmax as a slice of a larger scale buffer, off a 16-byte boundary."""
+    m, n, k = 1024, 16, 1024
+    host, (xd, qd, sd, cd) = make_case(m, n, k, seed=12)
+    big = torch.zeros(m + 8, dtype=torch.float32, device="cuda")
+    for off in (1, 3):
+        view = big[off:off + m]
+        view.copy_(sd)
+        assert view.data_ptr() % 16 != 0
+        for path in (_lib.PATH_STREAM, _lib.PATH_TSTREAM, _lib.PATH_UMMA):
+            st, out, holder = run_matmul((xd, qd, view, cd), m, n, k, cfg=_lib.TunaConfig(path=path))
+            assert st == 0
+            check_parity(out.cpu().numpy(), orc.matmul_ref(*host, m, n, k), TOL)
+
+
+def test_wrapper_on_two_streams_uses_separate_scratch():
+    """The reference-named `wrapper` may run on different streams at once (as the reference's can):
+    each stream gets its own scratch, so overlapping calls do not share arrival counters."""
+    m, n, k = 512, 16, 8192  # few tiles, every tile split across CTAs
+    lib = _lib.load()
+    cases = [make_case(m, n, k, 90 + i) for i in range(2)]
+    streams = [torch.cuda.Stream() for _ in range(2)]
+    outs = [torch.full((n, m), float("nan"), dtype=torch.float16, device="cuda") for _ in range(2)]
+    torch.cuda.synchronize()
+    for rep in range(8):
+        for i, s in enumerate(streams):
+            xd, qd, sd, cd = cases[i][1]
+            lib._Z7wrapperPvS_S_S_S_iiiP11CUstream_st(qd.data_ptr(), xd.data_ptr(), cd.data_ptr(), sd.data_ptr(),
+                                                      outs[i].data_ptr(), m, n, k, s.cuda_stream)
+            assert lib.tuna_last_wrapper_status() == 0
+    torch.cuda.synchronize()
+    for i in range(2):
+        check_parity(outs[i].cpu().numpy(), orc.matmul_ref(*cases[i][0], m, n, k), TOL)

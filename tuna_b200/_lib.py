@@ -33,7 +33,7 @@ class TunaConfig(ctypes.Structure):
         return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}
 
 
-PATH_AUTO, PATH_STREAM, PATH_UMMA = 0, 1, 2
+PATH_AUTO, PATH_STREAM, PATH_UMMA, PATH_TSTREAM = 0, 1, 2, 3
 
 # every symbol include/tuna_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {

@@ -16,7 +16,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libtuna_b200.so"
-SOURCES = ["tuna_api.cu", "host_util.cu", "dequant_sm100a.cu", "quantize_sm100a.cu", "gemm_stream_sm100a.cu", "gemm_umma_sm100a.cu", "ref_symbols.cu"]
+SOURCES = ["tuna_api.cu", "host_util.cu", "dequant_sm100a.cu", "quantize_sm100a.cu", "gemm_stream_sm100a.cu", "gemm_tstream_sm100a.cu", "gemm_umma_sm100a.cu", "ref_symbols.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
@@ -73,20 +73,5 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
-def build_microbench() -> Path:
-    """The stand-alone microbenchmark program behind the design notes (not part of the library)."""
-    out = HERE / "microbench_sm100a"
-    src = CSRC / "microbench_sm100a.cu"
-    if _stale(out, [src]):
-        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", str(out), str(src)]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode:
-            sys.stderr.write(r.stdout + r.stderr)
-            raise RuntimeError("nvcc failed on microbench_sm100a.cu")
-    return out
-
-
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
-    if "--microbench" in sys.argv:
-        print(build_microbench())

@@ -36,6 +36,35 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
+// The byte -> half2 dequantisation table: 256 entries (one per packed byte = two codes) at a
+// 256-byte stride, 32 copies of an entry side by side (one per bank), at a 64-KB-aligned
+// shared address.  ONE prmt then builds a lookup's whole address (table base | byte << 8 |
+// lane * 4, `lane_key` holding the first and last part) and every lookup is conflict free.
+constexpr int kLut64Bytes = 65536;
+
+__device__ __forceinline__ uint32_t lut_lookup(uint32_t w, uint32_t lane_key, uint32_t selector)
+{
+    // result bytes: [0] = lane*4, [1] = the selected byte of w, [2..3] = upper address bytes
+    uint32_t addr, v;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(addr) : "r"(w), "r"(lane_key), "r"(selector));
+    // not volatile: the table is constant once built, so the compiler may schedule lookups freely
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// 128-bit streaming load under a predicate (zeros when the predicate is false), without a branch.
+__device__ __forceinline__ uint4 ldg_stream_pred(const void *p, unsigned pred)
+{
+    uint4 v;
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %5, 0;\n"
+        " mov.b32 %0, 0;\n mov.b32 %1, 0;\n mov.b32 %2, 0;\n mov.b32 %3, 0;\n"
+        " @p ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];\n}"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+        : "l"(p), "r"(pred));
+    return v;
+}
+
 // Error word shared by the kernels that contain bounded waits.
 struct DeviceStatus {
     int code;      // 0 = ok, otherwise where a wait gave up

@@ -68,7 +68,6 @@ namespace tuna {
 
 constexpr int kStreamWarps = 16;
 constexpr int kStreamThreads = 32 * kStreamWarps;
-constexpr int kLut64Bytes = 65536;  // 256 entries x 256-byte stride (32 lanes x 4 bytes used)
 constexpr int kLoadsInFlight = 8;   // 128-bit weight loads in flight per lane
 
 struct StreamParams {
@@ -102,33 +101,10 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint32_t lut_lookup(uint32_t w, uint32_t lane_key, uint32_t selector)
-{
-    // result bytes: [0] = lane*4, [1] = the selected byte of w, [2..3] = upper address bytes
-    uint32_t addr, v;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(addr) : "r"(w), "r"(lane_key), "r"(selector));
-    // not volatile: the table is constant once built, so the compiler may schedule lookups freely
-    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
-
 // 16-byte asynchronous global -> shared copy; src_bytes = 0 fills the destination with zeros.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-
-// 128-bit streaming load under a predicate (zeros when the predicate is false), without a branch.
-__device__ __forceinline__ uint4 ldg_stream_pred(const void *p, unsigned pred)
-{
-    uint4 v;
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %5, 0;\n"
-        " mov.b32 %0, 0;\n mov.b32 %1, 0;\n mov.b32 %2, 0;\n mov.b32 %3, 0;\n"
-        " @p ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];\n}"
-        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-        : "l"(p), "r"(pred));
-    return v;
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr)
@@ -359,8 +335,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemm_stream_kernel(const St
             for (int rr = 0; rr < R; ++rr) {
                 const int row = tile_rt * 32 * R * WM + (wm * R + rr) * 32 + 4 * g;  // in matrix tile_b
                 if (row >= p.m) continue;  // m % 8 == 0 and the 4 rows sit inside one 8-row group
-                const float4 sc = *reinterpret_cast<const float4 *>(
+                // four scalar loads: absmax only has to be 4-byte aligned (a slice of a larger scale buffer)
+                const float *scp = reinterpret_cast<const float *>(
                     reinterpret_cast<const uint8_t *>(p.absmax) + (size_t)tile_b * (size_t)p.absmax_stride + (size_t)row * 4);
+                const float4 sc = make_float4(__ldg(scp), __ldg(scp + 1), __ldg(scp + 2), __ldg(scp + 3));
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -580,13 +558,17 @@ template <int R, int NT, bool BATCHED>
 static int launch_one_b(const StreamParams &p, int ctas, size_t smem, cudaStream_t stream)
 {
     static bool attr_set[64] = {false};  // one-time, per device, opt-in to large dynamic shared memory
+    static std::mutex mu;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TUNA_ERR_NO_DEVICE;
-    if (!attr_set[dev]) {
-        if (cudaFuncSetAttribute(gemm_stream_kernel<R, NT, BATCHED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kStreamSmemLimit) != cudaSuccess)
-            return TUNA_ERR_NO_DEVICE;
-        attr_set[dev] = true;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!attr_set[dev]) {
+            if (cudaFuncSetAttribute(gemm_stream_kernel<R, NT, BATCHED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kStreamSmemLimit) != cudaSuccess)
+                return TUNA_ERR_NO_DEVICE;
+            attr_set[dev] = true;
+        }
     }
     // Programmatic dependent launch: this grid may become resident while the previous kernel of
     // the stream is still draining; the kernel orders itself with griddepcontrol.wait.
@@ -609,7 +591,10 @@ static int launch_one(const StreamParams &p, int ctas, size_t smem, cudaStream_t
     return p.batch > 1 ? launch_one_b<R, NT, true>(p, ctas, smem, stream) : launch_one_b<R, NT, false>(p, ctas, smem, stream);
 }
 
-int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)
+// The launches of one GEMM (one per pass of tile_tok tokens) with the given scratch: `partials`
+// holds two partial tiles per CTA, `counters` one zeroed word per (row tile, warp slice).
+static int stream_launch_passes(const GemmArgs &a, const tuna_config &cfg, float *partials, unsigned int *counters,
+                                DeviceStatus *status)
 {
     const int nt = cfg.tile_tok / 8;
     StreamParams p;
@@ -619,14 +604,9 @@ int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)
     stream_geometry(a.m, a.k, cfg, nt, a.batch, &p);
     p.q_stride = (long long)a.q_stride; p.x_stride = (long long)a.x_stride;
     p.absmax_stride = (long long)a.absmax_stride; p.o_stride = (long long)a.o_stride;
-    p.status = device_status_word();
-    if (!p.status) return TUNA_ERR_NO_DEVICE;
-    const size_t counters = stream_counter_bytes(a.batch * p.row_tiles);
-    if (a.workspace == nullptr || a.workspace_bytes < gemm_stream_workspace_bytes(a.m, a.n, a.k, cfg, a.sm_count, a.batch))
-        return TUNA_ERR_WORKSPACE;
-    (void)counters;
-    p.partials = (float *)a.workspace;
-    p.counters = (unsigned int *)((uint8_t *)a.workspace + partial_region_bytes(a.sm_count));
+    p.status = status;
+    p.partials = partials;
+    p.counters = counters;
     int ctas = cfg.ctas;
     {   // no CTA with less than one block of prefetched steps
         const long long blocks = p.units * (cfg.k_steps / (kLoadsInFlight / cfg.rows_per_warp));
@@ -651,6 +631,33 @@ int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)
     return TUNA_OK;
 }
 
+int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg)
+{
+    DeviceStatus *status = device_status_word();
+    if (!status) return TUNA_ERR_NO_DEVICE;
+    if (a.workspace == nullptr || a.workspace_bytes < gemm_stream_workspace_bytes(a.m, a.n, a.k, cfg, a.sm_count, a.batch))
+        return TUNA_ERR_WORKSPACE;
+    return stream_launch_passes(a, cfg, (float *)a.workspace,
+                                (unsigned int *)((uint8_t *)a.workspace + partial_region_bytes(a.sm_count)), status);
+}
+
+// Scratch of the entry point that allocates nothing (below): its own compact layout,
+// [counters of this shape][two partial tiles per CTA of this configuration].
+size_t gemm_stream_compact_scratch_bytes(int m, int k, const tuna_config &c, size_t *counter_bytes)
+{
+    StreamParams geo;
+    const int nt = c.tile_tok / 8;
+    stream_geometry(m, k, c, nt, 1, &geo);
+    const size_t tile_floats = (size_t)c.warps_m * (c.rows_per_warp * 2 * nt * 4) * 32;
+    *counter_bytes = stream_counter_bytes(geo.row_tiles);
+    return *counter_bytes + 2 * (size_t)c.ctas * tile_floats * 4;
+}
+
+int launch_gemm_stream_compact(const GemmArgs &a, const tuna_config &cfg, void *scratch, size_t counter_bytes, DeviceStatus *status)
+{
+    return stream_launch_passes(a, cfg, (float *)((uint8_t *)scratch + counter_bytes), (unsigned int *)scratch, status);
+}
+
 }  // namespace tuna
 
 // ------------------------------------------------------------------ entry point that allocates nothing
@@ -663,17 +670,6 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[TUNA_NOALLOC_SC
 static __device__ __align__(256) tuna::DeviceStatus g_noalloc_status;
 
 namespace {
-// The array's own compact layout: [counters of this shape][partial tiles of this configuration].
-// The counters are cleared on the stream by every call, so shapes can alternate freely.
-size_t noalloc_scratch_bytes(int m, int k, const tuna_config &c)
-{
-    tuna::StreamParams geo;
-    const int nt = c.tile_tok / 8;
-    tuna::stream_geometry(m, k, c, nt, 1, &geo);
-    const size_t tile_floats = (size_t)c.warps_m * (c.rows_per_warp * 2 * nt * 4) * 32;
-    return tuna::stream_counter_bytes(geo.row_tiles) + 2 * (size_t)c.ctas * tile_floats * 4;
-}
-
 struct NoAllocDevice {
     bool ready = false;
     void *scratch = nullptr;
@@ -689,6 +685,7 @@ extern "C" int tuna_matmul_noalloc(const void *q, const void *x, const void *cod
     using namespace tuna;
     if (!q || !x || !code || !absmax || !o) return TUNA_ERR_NULL_POINTER;
     if (m <= 0 || k <= 0 || n <= 0 || (m % 8) || (k % 8)) return TUNA_ERR_BAD_SHAPE;
+    if ((long long)m * k / 2 > (1ll << 40)) return TUNA_ERR_TOO_LARGE;  // the same limit as tuna_matmul
     auto misaligned = [](const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) != 0; };
     if (misaligned(q, 16) || misaligned(x, 16) || misaligned(o, 16) || misaligned(absmax, 4) || misaligned(code, 4))
         return TUNA_ERR_MISALIGNED;
@@ -718,43 +715,14 @@ extern "C" int tuna_matmul_noalloc(const void *q, const void *x, const void *cod
         st = gemm_stream_normalize_config(m, n, k, sms, &c);
         if (st != TUNA_OK) return st;
     }
-    const size_t need = noalloc_scratch_bytes(m, k, c);
+    size_t counters = 0;
+    const size_t need = gemm_stream_compact_scratch_bytes(m, k, c, &counters);
     if (need > (size_t)TUNA_NOALLOC_SCRATCH_BYTES) return TUNA_ERR_TOO_LARGE;
-    StreamParams geo;
-    stream_geometry(m, k, c, c.tile_tok / 8, 1, &geo);
     // the counters must start at zero; the array keeps whatever the last call (or an aborted one) left
-    const size_t counters = stream_counter_bytes(geo.row_tiles);
     if (cudaMemsetAsync(d.scratch, 0, counters, (cudaStream_t)stream) != cudaSuccess) return TUNA_ERR_LAUNCH;
-    // same parameter block and launch as launch_gemm_stream, with the static arrays in place of a
-    // caller workspace and of the allocated status word
-    const int nt = c.tile_tok / 8;
-    StreamParams p;
-    std::memset(&p, 0, sizeof(p));
-    p.q = (const uint8_t *)q; p.x = (const __half *)x; p.code = (const float *)code; p.absmax = (const float *)absmax;
-    p.o = (__half *)o;
-    p.m = m; p.n = n; p.k = k;
-    stream_geometry(m, k, c, nt, 1, &p);
-    p.status = d.status;
-    p.counters = (unsigned int *)d.scratch;
-    p.partials = (float *)((uint8_t *)d.scratch + counters);
-    int ctas = c.ctas;
-    {
-        const long long blocks = p.units * (c.k_steps / (kLoadsInFlight / c.rows_per_warp));
-        if ((long long)ctas > blocks) ctas = (int)blocks;
-    }
-    if (!stream_split_steps(&p, ctas)) return TUNA_ERR_TOO_LARGE;
-    const size_t smem = stream_smem_bytes(p);
-    for (int tok0 = 0; tok0 < n; tok0 += c.tile_tok) {
-        p.tok0 = tok0;
-        switch (c.rows_per_warp * 10 + nt) {
-            case 11: st = launch_one<1, 1>(p, ctas, smem, (cudaStream_t)stream); break;
-            case 12: st = launch_one<1, 2>(p, ctas, smem, (cudaStream_t)stream); break;
-            case 14: st = launch_one<1, 4>(p, ctas, smem, (cudaStream_t)stream); break;
-            case 21: st = launch_one<2, 1>(p, ctas, smem, (cudaStream_t)stream); break;
-            case 22: st = launch_one<2, 2>(p, ctas, smem, (cudaStream_t)stream); break;
-            default: return TUNA_ERR_BAD_CONFIG;
-        }
-        if (st != TUNA_OK) return st;
-    }
-    return TUNA_OK;
+    GemmArgs a;
+    a.q = (const uint8_t *)q; a.x = x; a.code = (const float *)code; a.absmax = (const float *)absmax; a.o = o;
+    a.m = m; a.n = n; a.k = k; a.workspace = nullptr; a.workspace_bytes = 0;
+    a.stream = (cudaStream_t)stream; a.sm_count = sms;
+    return launch_gemm_stream_compact(a, c, d.scratch, counters, d.status);
 }

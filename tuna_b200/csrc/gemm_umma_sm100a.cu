@@ -40,11 +40,11 @@
 #include "common.cuh"
 #include "launchers.h"
 #include "sm100_ptx.cuh"
+#include "tcgen05.cuh"
 
 namespace tuna {
 
 constexpr int kChunkK = 64;                    // K extent of one pipeline stage
-constexpr int kBlockRows = 128;                // rows of one MMA (TMEM lanes)
 constexpr int kWBlockBytes = kBlockRows * kChunkK / 2;  // 4096: packed bytes of one block-stage
 constexpr int kSlotCols = kChunkK / 2;         // 32 TMEM columns hold one block-stage of fp16 A
 constexpr int kUmmaLutBytes = 256 * 32 * 4;
@@ -72,67 +72,12 @@ struct UmmaParams {
     int dq_groups;
 };
 
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// D[tmem] (+)= A[tmem] * B[smem desc]
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate)
-{
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_st_x32(uint32_t taddr, const uint32_t (&v)[32])
-{
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-        ::"r"(taddr),
-        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
-        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
-        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_ld_x16(uint32_t taddr, float (&v)[16])
-{
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
 // Shared-memory matrix descriptor of a K-major operand tile stored with the 128-byte swizzle:
 // rows of 64 fp16 (128 bytes), 8-row groups 1024 bytes apart (stride byte offset), version 1,
 // layout type 2 (SWIZZLE_128B).  Advancing K by 16 elements adds 32 bytes to the start address.
 __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr)
 {
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-
-// Instruction descriptor, kind::f16: D fp32 (bits 4-5 = 1), A and B fp16 (0), both K-major,
-// N >> 3 at bits 17-22, M >> 4 at bits 24-28.
-__host__ __device__ constexpr uint32_t make_idesc(int n_tile)
-{
-    return (1u << 4) | ((uint32_t)(n_tile >> 3) << 17) | ((uint32_t)(kBlockRows >> 4) << 24);
 }
 
 // Which weight row a TMEM lane holds.  Lane 32*quarter + l of a 128-row block takes row
@@ -584,12 +529,18 @@ template <int N_TILE>
 static int launch_umma(const UmmaParams &p, const CUtensorMap &mq, const CUtensorMap &mx, int ctas, int threads,
                        size_t smem, cudaStream_t stream)
 {
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(gemm_w4a16_umma_kernel<N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 225 * 1024) != cudaSuccess)
-            return TUNA_ERR_NO_DEVICE;
-        attr_set = true;
+    static bool attr_set[64] = {false};  // one-time, per device, opt-in to large dynamic shared memory
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TUNA_ERR_NO_DEVICE;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!attr_set[dev]) {
+            if (cudaFuncSetAttribute(gemm_w4a16_umma_kernel<N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     225 * 1024) != cudaSuccess)
+                return TUNA_ERR_NO_DEVICE;
+            attr_set[dev] = true;
+        }
     }
     gemm_w4a16_umma_kernel<N_TILE><<<ctas, threads, smem, stream>>>(p, mq, mx);
     return cudaGetLastError() == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;

@@ -49,10 +49,18 @@ cudaError_t launch_dequant(const void *q, const void *absmax, const void *code, 
 int launch_gemm_stream(const GemmArgs &a, const tuna_config &cfg);
 size_t gemm_stream_workspace_bytes(int m, int n, int k, const tuna_config &cfg, int sm_count, int batch = 1);
 int gemm_stream_normalize_config(int m, int n, int k, int sm_count, tuna_config *cfg);
+// The same launches with a caller-provided scratch in a compact layout ([counters][partial tiles]).
+size_t gemm_stream_compact_scratch_bytes(int m, int k, const tuna_config &cfg, size_t *counter_bytes);
+int launch_gemm_stream_compact(const GemmArgs &a, const tuna_config &cfg, void *scratch, size_t counter_bytes, DeviceStatus *status);
 
 // tcgen05/TMEM kernel.  Returns a tuna_status.
 int launch_gemm_umma(const GemmArgs &a, const tuna_config &cfg);
 size_t gemm_umma_workspace_bytes(int m, int n, int k, const tuna_config &cfg, int sm_count);
 int gemm_umma_normalize_config(int m, int n, int k, int sm_count, tuna_config *cfg);
+
+// tcgen05 weight-streaming kernel (small token counts).  Returns a tuna_status.
+int launch_gemm_tstream(const GemmArgs &a, const tuna_config &cfg);
+size_t gemm_tstream_workspace_bytes(int m, int n, int k, const tuna_config &cfg, int sm_count);
+int gemm_tstream_normalize_config(int m, int n, int k, int sm_count, tuna_config *cfg);
 
 }  // namespace tuna

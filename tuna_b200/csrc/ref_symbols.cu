@@ -5,39 +5,49 @@
 // gets the sm_100a kernels with no source change.
 //
 // The reference has no workspace argument (its split-K accumulates into `o` with fp16 atomics,
-// kernel.cu:2739-2745) and reports no errors.  Here the workspace is one cached allocation per
-// device, grown on demand and zero-filled once; the status of the last call of the calling
-// thread can be read with tuna_last_wrapper_status().
+// kernel.cu:2739-2745) and reports no errors.  Here the workspace is a cached allocation per
+// (device, stream) - the reference's wrapper may run concurrently on different streams, and two
+// overlapping calls must not share arrival counters - zero-filled on that stream when it is
+// created.  A buffer that has been handed to a launch is never freed (an earlier call or a
+// captured graph may still refer to it): when a larger one is needed the old one is kept.
+// Allocation is impossible while the stream is being captured; the call then fails with
+// TUNA_ERR_WORKSPACE unless an earlier, uncaptured call on that stream already created a large
+// enough buffer.  The status of the calling thread's last call can be read with
+// tuna_last_wrapper_status().
 #include <cuda_runtime.h>
+#include <map>
 #include <mutex>
+#include <utility>
+#include <vector>
 #include "../../include/tuna_b200.h"
 
 namespace {
 
-struct DeviceScratch {
+struct StreamScratch {
     void *ptr = nullptr;
     size_t bytes = 0;
 };
-DeviceScratch g_scratch[64];
+std::map<std::pair<int, cudaStream_t>, StreamScratch> g_scratch;
+std::vector<void *> g_retired;  // outgrown buffers, kept alive on purpose
 std::mutex g_scratch_mutex;
 thread_local int t_last_status = TUNA_OK;
 
-// The cached workspace of the current device, at least `need` bytes.  Growing it waits for the
-// device (the old buffer may be in use by an earlier call) - a rare, one-time cost per size.
-void *scratch_for(size_t need, size_t *bytes)
+// The cached workspace of (current device, stream), at least `need` bytes.
+void *scratch_for(size_t need, cudaStream_t stream, size_t *bytes)
 {
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
     std::lock_guard<std::mutex> lock(g_scratch_mutex);
-    DeviceScratch &s = g_scratch[dev];
+    StreamScratch &s = g_scratch[std::make_pair(dev, stream)];
     if (s.bytes < need) {
-        if (cudaDeviceSynchronize() != cudaSuccess) return nullptr;
-        if (s.ptr) cudaFree(s.ptr);
-        s.ptr = nullptr;
-        s.bytes = 0;
-        size_t want = need < (size_t(32) << 20) ? (size_t(32) << 20) : need;
-        if (cudaMalloc(&s.ptr, want) != cudaSuccess) { s.ptr = nullptr; return nullptr; }
-        if (cudaMemset(s.ptr, 0, want) != cudaSuccess) { cudaFree(s.ptr); s.ptr = nullptr; return nullptr; }
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+        const size_t want = need < (size_t(32) << 20) ? (size_t(32) << 20) : need;
+        void *p = nullptr;
+        if (cudaMalloc(&p, want) != cudaSuccess) return nullptr;
+        if (cudaMemsetAsync(p, 0, want, stream) != cudaSuccess) { cudaFree(p); return nullptr; }  // never launched on: safe to free
+        if (s.ptr) g_retired.push_back(s.ptr);
+        s.ptr = p;
         s.bytes = want;
     }
     *bytes = s.bytes;
@@ -52,7 +62,7 @@ void wrapper(void *q, void *x, void *c, void *s, void *o, int m, int n, int k, c
     const size_t need = tuna_matmul_workspace_bytes(m, n, k);
     if (need == 0) { t_last_status = TUNA_ERR_BAD_SHAPE; return; }
     size_t bytes = 0;
-    void *ws = scratch_for(need, &bytes);
+    void *ws = scratch_for(need, stream, &bytes);
     if (!ws) { t_last_status = TUNA_ERR_WORKSPACE; return; }
     t_last_status = tuna_matmul(q, x, c, s, o, m, n, k, ws, bytes, (void *)stream);
 }

@@ -61,6 +61,7 @@ static int resolve_config(int m, int n, int k, int sm_count, const tuna_config *
     int st;
     if (c.path == TUNA_PATH_STREAM) st = gemm_stream_normalize_config(m, n, k, sm_count, &c);
     else if (c.path == TUNA_PATH_UMMA) st = gemm_umma_normalize_config(m, n, k, sm_count, &c);
+    else if (c.path == TUNA_PATH_TSTREAM) st = gemm_tstream_normalize_config(m, n, k, sm_count, &c);
     else st = TUNA_ERR_BAD_CONFIG;
     if (st != TUNA_OK) return st;
     *out = c;
@@ -78,8 +79,16 @@ static bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_
 
 static size_t workspace_for(int m, int n, int k, const tuna_config &c, int sm_count)
 {
-    return c.path == TUNA_PATH_STREAM ? gemm_stream_workspace_bytes(m, n, k, c, sm_count)
-                                      : gemm_umma_workspace_bytes(m, n, k, c, sm_count);
+    if (c.path == TUNA_PATH_STREAM) return gemm_stream_workspace_bytes(m, n, k, c, sm_count);
+    if (c.path == TUNA_PATH_TSTREAM) return gemm_tstream_workspace_bytes(m, n, k, c, sm_count);
+    return gemm_umma_workspace_bytes(m, n, k, c, sm_count);
+}
+
+static int launch_gemm(const GemmArgs &a, const tuna_config &c)
+{
+    if (c.path == TUNA_PATH_STREAM) return launch_gemm_stream(a, c);
+    if (c.path == TUNA_PATH_TSTREAM) return launch_gemm_tstream(a, c);
+    return launch_gemm_umma(a, c);
 }
 
 }  // namespace tuna
@@ -106,7 +115,7 @@ extern "C" int tuna_matmul_cfg(const void *q, const void *x, const void *code, c
     a.q = (const uint8_t *)q; a.x = x; a.code = (const float *)code; a.absmax = (const float *)absmax; a.o = o;
     a.m = m; a.n = n; a.k = k; a.workspace = workspace; a.workspace_bytes = workspace_bytes;
     a.stream = (cudaStream_t)stream; a.sm_count = sms;
-    return c.path == TUNA_PATH_STREAM ? launch_gemm_stream(a, c) : launch_gemm_umma(a, c);
+    return launch_gemm(a, c);
 }
 
 extern "C" int tuna_matmul_batched(const void *q, const void *x, const void *code, const void *absmax, void *o,
@@ -136,7 +145,7 @@ extern "C" int tuna_matmul_batched(const void *q, const void *x, const void *cod
         a.batch = batch; a.q_stride = q_stride; a.x_stride = x_stride; a.absmax_stride = absmax_stride; a.o_stride = o_stride;
         return launch_gemm_stream(a, c);
     }
-    // token counts of the tensor-core kernel: one launch per matrix
+    // the tcgen05 kernels: one launch per matrix
     const size_t need = workspace_for(m, n, k, c, sms);
     if (workspace == nullptr || workspace_bytes < need) return TUNA_ERR_WORKSPACE;
     for (int b = 0; b < batch; ++b) {
@@ -144,7 +153,7 @@ extern "C" int tuna_matmul_batched(const void *q, const void *x, const void *cod
         a.x = (const uint8_t *)x + (size_t)b * x_stride;
         a.absmax = (const float *)((const uint8_t *)absmax + (size_t)b * absmax_stride);
         a.o = (uint8_t *)o + (size_t)b * o_stride;
-        st = launch_gemm_umma(a, c);
+        st = launch_gemm(a, c);
         if (st != TUNA_OK) return st;
     }
     return TUNA_OK;

@@ -33,7 +33,7 @@
 //                split-K partials and fix-up
 //   warps 8-23   dequant: 128-bit ld.global.nc into an 8-deep register ring -> prmt + ld.shared
 //                table lookups -> tcgen05.st into the A slots.  Warp (quarter q, group j)
-//                handles rows 32q..+31 and step j (32 columns) of every 128x128 slot.
+//                handles rows 32q..+31 of the 128x128 slots j, j+4, j+8, ... of the CTA.
 // The scale is constant along K (one block per row, test.py:81, kernel.cu:2178-2180) and is
 // applied once, in fp32, to the accumulated sum.
 //
@@ -58,13 +58,39 @@
 #include "sm100_ptx.cuh"
 #include "tcgen05.cuh"
 
+// Optional per-warp timing (debug builds with -DTUNA_TS_PROFILE only): absolute times of the
+// warp's milestones and the clocks it spent in each kind of wait.
+#ifdef TUNA_TS_PROFILE
+__device__ long long g_ts_prof[160 * 24 * 8];
+__device__ __forceinline__ long long ts_gtime()
+{
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TS_PROF_DECL long long pw_[4] = {0, 0, 0, 0}, pt_ = 0, pg_[4] = {ts_gtime(), 0, 0, 0}; (void)pt_;
+#define TS_PROF_MARK(i) pg_[i] = ts_gtime();
+#define TS_PROF_BEGIN pt_ = clock64();
+#define TS_PROF_END(i) pw_[i] += clock64() - pt_;
+#define TS_PROF_STORE                                                                     \
+    if ((threadIdx.x & 31) == 0) {                                                        \
+        long long *d_ = g_ts_prof + ((size_t)blockIdx.x * 24 + (threadIdx.x >> 5)) * 8;   \
+        for (int i_ = 0; i_ < 4; ++i_) { d_[i_] = pg_[i_]; d_[4 + i_] = pw_[i_]; }        \
+    }
+#else
+#define TS_PROF_DECL
+#define TS_PROF_MARK(i)
+#define TS_PROF_BEGIN
+#define TS_PROF_END(i)
+#define TS_PROF_STORE
+#endif
+
 namespace tuna {
 
 constexpr int kTsChunkK = 128;        // K extent of a unit / an A slot
 constexpr int kTsSlotCols = 64;       // tensor-memory columns of one A slot (128 rows x 128 fp16)
-constexpr int kTsASlots = 6;          // A-slot ring
+constexpr int kTsMaxASlots = 8;       // A-slot ring: as many as the accumulators leave room for (6 or 7)
 constexpr int kTsAccCols = 64;        // columns of one accumulator buffer (row_blocks * tile_tok <= 64)
-constexpr int kTsABase = 2 * kTsAccCols;
 constexpr int kTsTmemCols = 512;
 constexpr int kTsMaxXStages = 6;
 constexpr int kTsLoads = 8;           // 128-bit weight loads in flight per lane
@@ -85,6 +111,9 @@ struct TsParams {
     int m, n, k;
     int tok0;         // first token of this pass
     int row_blocks;   // RB: 128-row blocks per tile
+    int a_slots;      // A-slot ring depth
+    int a_base;       // first tensor-memory column of the A slots (behind the two accumulator buffers)
+    int acc_cols;     // columns of one accumulator buffer
     int chunks;       // ceil(k / 128)
     int row_tiles;    // ceil(m / (128 RB))
     int units;        // row_tiles * chunks
@@ -107,10 +136,11 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr int kXS = N_TILE == 64 ? 3 : 6;   // activation stages (48 KB at most)
     constexpr int kLag = N_TILE == 64 ? 1 : 3;  // units between issuing a stage's copies and handing it over
-    __shared__ __align__(8) uint64_t bars[2 * kTsASlots + 2 * kTsMaxXStages + 4];
+    __shared__ __align__(8) uint64_t bars[2 * kTsMaxASlots + 2 * kTsMaxXStages + 4];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
+    TS_PROF_DECL
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
     const int cta = blockIdx.x;
     const int RB = p.row_blocks;
@@ -124,8 +154,8 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     const uint32_t lut_addr = (xring + kXS * kXStageBytes + 0xFFFFu) & ~0xFFFFu;
 
     const uint32_t bar0 = smem_u32(&bars[0]);
-    const uint32_t a_full = bar0, a_empty = a_full + 8 * kTsASlots;
-    const uint32_t x_full = a_empty + 8 * kTsASlots, x_empty = x_full + 8 * kXS;
+    const uint32_t a_full = bar0, a_empty = a_full + 8 * kTsMaxASlots;
+    const uint32_t x_full = a_empty + 8 * kTsMaxASlots, x_empty = x_full + 8 * kXS;
     const uint32_t d_full = x_empty + 8 * kXS, d_empty = d_full + 16;
     volatile int *abort_flag = &s_abort;
 
@@ -136,7 +166,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int i = 0; i < kTsASlots; ++i) { mbar_init(a_full + 8 * i, kTsDequantWarps); mbar_init(a_empty + 8 * i, 1); }
+        for (int i = 0; i < kTsMaxASlots; ++i) { mbar_init(a_full + 8 * i, 4); mbar_init(a_empty + 8 * i, 1); }
         for (int i = 0; i < kXS; ++i) { mbar_init(x_full + 8 * i, 1); mbar_init(x_empty + 8 * i, 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(d_full + 8 * i, 1); mbar_init(d_empty + 8 * i, 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -168,6 +198,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         tc_fence_before();
         __syncthreads();
         tc_fence_after();
+        TS_PROF_MARK(1)
         return s_tmem_base;
     };
     uint32_t tmem = 0;
@@ -184,18 +215,29 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         for (int u = 0; u < n_units; ++u) {
             const bool seg_last = (chunk + 1 == p.chunks) || (u + 1 == n_units);
             bool ok = true;
+            TS_PROF_BEGIN
             if (seg_first) ok = mbar_wait(d_empty + 8 * rd.idx, rd.phase ^ 1, abort_flag, p.status, 3);
+            TS_PROF_END(0)
+            TS_PROF_BEGIN
             ok = ok && mbar_wait(x_full + 8 * rx.idx, rx.phase, abort_flag, p.status, 4);
             if (!__all_sync(0xffffffffu, ok)) break;
+            TS_PROF_END(1)
             const uint32_t xbase = xring + (uint32_t)rx.idx * kXStageBytes;
-            const uint32_t dbase = tmem + (uint32_t)rd.idx * kTsAccCols;
+            const uint32_t dbase = tmem + (uint32_t)(rd.idx * p.acc_cols);
             for (int rb = 0; rb < RB; ++rb) {
+                TS_PROF_BEGIN
                 if (!mbar_wait_warp(a_full + 8 * ra.idx, ra.phase, abort_flag, p.status, 5)) { ok = false; break; }
+                TS_PROF_END(2)
                 tc_fence_after();
+                TS_PROF_BEGIN
                 if (elect_one_sync()) {
-                    const uint32_t abase = tmem + kTsABase + (uint32_t)ra.idx * kTsSlotCols;
+                    const uint32_t abase = tmem + (uint32_t)p.a_base + (uint32_t)ra.idx * kTsSlotCols;
 #pragma unroll
+#ifdef TS_ABL_NOMMA  // timing experiment: commits only
+                    for (int mm = 0; mm < 0; ++mm) {
+#else
                     for (int mm = 0; mm < 8; ++mm) {  // step mm/2, 16-wide MMA mm%2
+#endif
                         const uint64_t bdesc = make_desc_noswizzle(xbase + mm * kBTileBytes, kLbo, kSbo);
                         tc_mma_ts(dbase + (uint32_t)rb * N_TILE, abase + mm * 8, bdesc, idesc, (seg_first && mm == 0) ? 0u : 1u);
                     }
@@ -206,7 +248,8 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
                     }
                 }
                 __syncwarp();
-                ra.advance(kTsASlots);
+                TS_PROF_END(3)
+                ra.advance(p.a_slots);
             }
             if (!ok) break;
             rx.advance(kXS);
@@ -225,7 +268,27 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         Ring rx, rdone;
         int chunk = chunk0;
         const int tok_lo = lane & 7, t_lo = (lane >> 3) & 1, rest_lo = lane >> 4;
-        const uint32_t dst_lane = (uint32_t)tok_lo * 16 + (uint32_t)t_lo * 8;
+        // per copy i: source offset in halfs relative to x[tok0][k0] (-1: token past n), its
+        // column inside the chunk, and the destination offset inside a stage - all independent of
+        // the unit.  Kept in registers for the 16-token tile (whose units are the shortest).
+        const __half *x_pass = p.x + (size_t)p.tok0 * p.k;
+        auto copy_params = [&](int i, int &src_off, int &col, uint32_t &dst) {
+            const int rest = (i & ~1) + rest_lo, uu = i & 1;
+            const int t_hi = rest & 1, step = (rest >> 1) & 3, ng = rest >> 3;
+            const int tok = ng * 8 + tok_lo;
+            col = 32 * step + 8 * (2 * t_hi + t_lo);
+            src_off = p.tok0 + tok < p.n ? tok * p.k + col + 4 * uu : -1;
+            // B tile (step, u): [t/2][tok/8][tok%8][16 bytes]; columns col + 4u .. +3 of the
+            // 8-column weight tile go to MMA u, at byte 8*(t%2) of the token's row
+            dst = (uint32_t)(2 * step + uu) * kBTileBytes + (uint32_t)t_hi * kLbo + (uint32_t)ng * kSbo + (uint32_t)tok_lo * 16 + (uint32_t)t_lo * 8;
+        };
+        constexpr bool kHoist = N_TILE == 16;
+        int src_off[kHoist ? N_TILE : 1], col_off[kHoist ? N_TILE : 1];
+        uint32_t dst_off[kHoist ? N_TILE : 1];
+        if (kHoist) {
+#pragma unroll
+            for (int i = 0; i < N_TILE; ++i) copy_params(i, src_off[i], col_off[i], dst_off[i]);
+        }
         auto hand_over = [&]() {
             // this lane's copies of the oldest unit have landed; generic-proxy writes -> visible
             // to the tensor core's (async proxy) reads; then one arrival for the warp
@@ -236,25 +299,34 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         };
         bool ok = true;
         for (int u = 0; u < n_units; ++u) {
+            TS_PROF_BEGIN
             if (!mbar_wait_warp(x_empty + 8 * rx.idx, rx.phase ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
+            TS_PROF_END(0)
             const uint32_t stage = xring + (uint32_t)rx.idx * kXStageBytes;
             const int k0 = chunk * kTsChunkK;
-#pragma unroll 4
-            for (int i = 0; i < N_TILE; ++i) {
-                const int rest = (i & ~1) + rest_lo, uu = i & 1;
-                const int t_hi = rest & 1, step = (rest >> 1) & 3, ng = rest >> 3;
-                const int tok = p.tok0 + ng * 8 + tok_lo;
-                const int col = k0 + 32 * step + 8 * (2 * t_hi + t_lo);
-                const bool in = tok < p.n && col < p.k;
-                // B tile (step, u): [t/2][tok/8][tok%8][16 bytes]; columns col + 4u .. +3 of the
-                // 8-column weight tile go to MMA u, at byte 8*(t%2) of the token's row
-                const uint32_t dst = stage + (uint32_t)(2 * step + uu) * kBTileBytes + (uint32_t)t_hi * kLbo + (uint32_t)ng * kSbo + dst_lane;
-                const __half *src = in ? p.x + (size_t)tok * p.k + col + 4 * uu : p.x;
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(in ? 8u : 0u) : "memory");
+            const __half *xk = x_pass + k0;
+            auto copy_one = [&](int so, int co, uint32_t dd) {
+                const bool in = so >= 0 && k0 + co < p.k;
+                const __half *src = in ? xk + so : p.x;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(stage + dd), "l"(src), "r"(in ? 8u : 0u) : "memory");
+            };
+            if constexpr (kHoist) {
+#pragma unroll
+                for (int i = 0; i < N_TILE; ++i) copy_one(src_off[i], col_off[i], dst_off[i]);
+            } else {
+#pragma unroll 8
+                for (int i = 0; i < N_TILE; ++i) {
+                    int so, co;
+                    uint32_t dd;
+                    copy_params(i, so, co, dd);
+                    copy_one(so, co, dd);
+                }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
             if (u >= kLag) {
+                TS_PROF_BEGIN
                 asm volatile("cp.async.wait_group %0;" ::"n"(kLag) : "memory");
+                TS_PROF_END(1)
                 hand_over();
             }
             rx.advance(kXS);
@@ -267,7 +339,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
     } else if (warp < kTsEpilogueWarp0) {
-        tmem = finish_prologue();  // idle warps of the control warpgroup
+        tmem = finish_prologue();  // idle warps
     } else if (warp < kTsDequantWarp0) {
         // ------------------------------------------------------------------ epilogue
         tmem = finish_prologue();
@@ -281,8 +353,11 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
             const int c0 = chunk;
             const int c1 = min(p.chunks, c0 + (n_units - u));
             const bool full = (c0 == 0 && c1 == p.chunks);
+            TS_PROF_BEGIN
             if (!mbar_wait_warp(d_full + 8 * rd.idx, rd.phase, abort_flag, p.status, 6)) break;
+            TS_PROF_END(0)
             tc_fence_after();
+            TS_PROF_BEGIN
             float *my_partial = p.partials + (size_t)(2 * cta + (c0 == 0 ? 1 : 0)) * slot_floats;
             for (int rb = 0; rb < RB; ++rb) {
                 const int row = (tile * RB + rb) * kBlockRows + row_in_block;
@@ -290,7 +365,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
 #pragma unroll 1
                 for (int piece = 0; piece < N_TILE / 16; ++piece) {
                     float v[16];
-                    tc_ld_x16(tmem + ((uint32_t)(32 * quarter) << 16) + (uint32_t)rd.idx * kTsAccCols + (uint32_t)rb * N_TILE + piece * 16, v);
+                    tc_ld_x16(tmem + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(rd.idx * p.acc_cols) + (uint32_t)rb * N_TILE + piece * 16, v);
                     if (full) {
                         if (row < p.m) {
 #pragma unroll
@@ -368,6 +443,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
                     }
                 }
             }
+            TS_PROF_END(1)
             u += c1 - c0;
             chunk = 0;
             ++tile;
@@ -375,68 +451,119 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         }
     } else {
         // ------------------------------------------------------------------ dequant
-        // position and first loads before anything else (the weights are constants; nothing
-        // another kernel writes is touched before griddepcontrol.wait)
-        const int group = (warp - kTsDequantWarp0) >> 2;  // the 32-column step of every slot this warp converts
+        // Group j (4 warps, one per 32-lane quarter) converts the slots j, j+4, j+8, ... of this CTA
+        // whole: 4 steps = 4 loads per lane per slot, one wait / fence / arrival per slot.  The four
+        // groups work on four different slots at once, so the latency of a slot's chain (lookups ->
+        // tcgen05.st -> wait::st -> arrive) is overlapped four times.
+        // Position and first loads before anything else (the weights are constants; nothing another
+        // kernel writes is touched before griddepcontrol.wait).
+        const int group = (warp - kTsDequantWarp0) >> 2;
         const int g = lane >> 2, t = lane & 3;
         const int n_rg = p.m >> 3;
         const size_t rg_bytes = row_group_bytes(p.k);
-        // prefetch cursor over this CTA's slots: (tile, chunk, rb)
-        int pf_tile = tile0, pf_chunk = chunk0, pf_rb = 0, pf_idx = 0;
-        auto next_load = [&]() -> uint4 {
-            const int rg = (pf_tile * RB + pf_rb) * 16 + 4 * quarter + (g >> 1);
-            const int col = pf_chunk * kTsChunkK + 32 * group + 8 * t;
-            const bool in = pf_idx < total_slots && rg < n_rg && col < p.k;
-            const uint8_t *src = p.q + (in ? (size_t)rg * rg_bytes + (size_t)col * 4 + (g & 1) * 16 : 0);
-            ++pf_idx;
-            if (++pf_rb == RB) {
-                pf_rb = 0;
-                if (++pf_chunk == p.chunks) { pf_chunk = 0; ++pf_tile; }
-            }
-            return ldg_stream_pred(src, in ? 1u : 0u);
+        const int A = p.a_slots;
+        // Cursor of the next slot to prefetch.  The group's slots are 4 apart in the CTA's slot
+        // sequence: with RB in {1, 2, 4} that is always the same row block of the tile
+        // (rb = group % RB) and 4 / RB units further on - no division in the loop.
+        const int rb = group % RB, ustep = 4 / RB;
+        int pf_unit = group / RB;
+        int pf_tile = (u_begin + pf_unit) / p.chunks, pf_chunk = (u_begin + pf_unit) - pf_tile * p.chunks;
+        const int lane_rg = 4 * quarter + (g >> 1);
+        const uint32_t lane_off = (uint32_t)(8 * t) * 4 + (g & 1) * 16;
+        // source and predicate mask (bit st = step st) of this lane's 4 loads of the slot at the
+        // cursor; advances the cursor
+        auto prefetch_prepare = [&](unsigned &mask) -> const uint8_t * {
+            const int rg = (pf_tile * RB + rb) * 16 + lane_rg;
+            const int col = pf_chunk * kTsChunkK + 8 * t;
+            const int steps_in = min((p.k - col + 31) >> 5, 4);  // steps whose 8-column tile starts before k
+            const bool in = pf_unit < n_units && rg < n_rg;
+            mask = in ? (1u << steps_in) - 1u : 0u;
+            const uint8_t *src = p.q + (in ? (size_t)rg * rg_bytes + (size_t)pf_chunk * (kTsChunkK * 4) + lane_off : 0);
+            pf_unit += ustep;
+            pf_chunk += ustep;
+            while (pf_chunk >= p.chunks) { pf_chunk -= p.chunks; ++pf_tile; }
+            return src;
         };
-        uint4 ring[kTsLoads];
+        uint4 ring[2][4];
 #pragma unroll
-        for (int i = 0; i < kTsLoads; ++i) ring[i] = next_load();
+        for (int h = 0; h < 2; ++h) {
+            unsigned mask;
+            const uint8_t *src = prefetch_prepare(mask);
+#pragma unroll
+            for (int st = 0; st < 4; ++st) ring[h][st] = ldg_stream_pred(src + (mask ? st * 128 : 0), (mask >> st) & 1u);
+        }
         tmem = finish_prologue();
         const uint32_t lane_key = (lut_addr & 0xFFFF0000u) | (uint32_t)(lane * 4);
-        const uint32_t a_lane0 = tmem + ((uint32_t)(32 * quarter) << 16) + kTsABase + 16u * (uint32_t)group;
-        Ring ra;
+        const uint32_t a_lane0 = tmem + ((uint32_t)(32 * quarter) << 16) + (uint32_t)p.a_base;
+        int a_idx = group;      // ring position of slot `sl`: sl % A, parity of its use (sl / A) & 1
+        uint32_t a_phase = 0;
         bool ok = true;
-        for (int base = 0; ok && base < total_slots; base += kTsLoads) {
+#ifdef TUNA_TS_PROFILE
+        const long long loop_c0 = clock64();
+#endif
+        for (int sl = group; ok && sl < total_slots; sl += 8) {
 #pragma unroll
-            for (int i = 0; i < kTsLoads; ++i) {
-                if (base + i >= total_slots) break;
-                const uint4 wv = ring[i];
-                ring[i] = next_load();
-                const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};  // word r = row 4(g%2)+r, byte c = column pair c
-                if (!mbar_wait_warp(a_empty + 8 * ra.idx, ra.phase ^ 1, abort_flag, p.status, 7)) { ok = false; break; }
+            for (int h = 0; h < 2; ++h) {
+                if (sl + 4 * h >= total_slots) break;
+                TS_PROF_BEGIN
+                if (!mbar_wait_warp(a_empty + 8 * a_idx, a_phase ^ 1, abort_flag, p.status, 7)) { ok = false; break; }
+                TS_PROF_END(0)
                 tc_fence_after();
-                const uint32_t ta = a_lane0 + (uint32_t)ra.idx * kTsSlotCols;
+                TS_PROF_BEGIN
+                const uint32_t ta = a_lane0 + (uint32_t)a_idx * kTsSlotCols;
+                unsigned pf_mask;
+                const uint8_t *pf_src = prefetch_prepare(pf_mask);  // the slot two ahead of this one
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {  // rows 2h, 2h+1 -> lanes +16h
-                    uint32_t v[2][4];
+                for (int st = 0; st < 4; ++st) {
+                    const uint4 wv = ring[h][st];
+#ifndef TS_ABL_NOLDG
+                    ring[h][st] = ldg_stream_pred(pf_src + (pf_mask ? st * 128 : 0), (pf_mask >> st) & 1u);
+#else
+                    ring[h][st].x += (uint32_t)(size_t)pf_src;  // timing experiment: no global loads
+#endif
+                    const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};  // word r = row 4(g%2)+r, byte c = column pair c
+                    uint32_t v[4][4];  // the step's 16 lookups in flight together
 #pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        v[r][0] = lut_lookup(w[2 * h + r], lane_key, 0x7604);
-                        v[r][1] = lut_lookup(w[2 * h + r], lane_key, 0x7614);
-                        v[r][2] = lut_lookup(w[2 * h + r], lane_key, 0x7624);
-                        v[r][3] = lut_lookup(w[2 * h + r], lane_key, 0x7634);
+                    for (int r = 0; r < 4; ++r) {
+#ifdef TS_ABL_NOLUT  // timing experiment: no table lookups
+                        v[r][0] = w[r]; v[r][1] = w[r] + lane_key; v[r][2] = w[r] ^ lane_key; v[r][3] = w[r] >> 1;
+#else
+                        v[r][0] = lut_lookup(w[r], lane_key, 0x7604);
+                        v[r][1] = lut_lookup(w[r], lane_key, 0x7614);
+                        v[r][2] = lut_lookup(w[r], lane_key, 0x7624);
+                        v[r][3] = lut_lookup(w[r], lane_key, 0x7634);
+#endif
                     }
-                    tc_st_16x256b_x2(ta + ((uint32_t)(16 * h) << 16), v[0][0], v[0][1], v[1][0], v[1][1], v[0][2], v[0][3], v[1][2], v[1][3]);
+                    // rows 0, 1 -> lanes g, g+8; rows 2, 3 -> lanes g+16, g+24
+#ifdef TS_ABL_NOST  // timing experiment: keep the lookups alive, skip the stores
+                    asm volatile("" ::"r"(v[0][0] ^ v[0][1] ^ v[0][2] ^ v[0][3] ^ v[1][0] ^ v[1][1] ^ v[1][2] ^ v[1][3] ^ v[2][0] ^ v[2][1] ^ v[2][2] ^ v[2][3] ^ v[3][0] ^ v[3][1] ^ v[3][2] ^ v[3][3]), "r"(ta));
+#else
+                    tc_st_16x256b_x2(ta + 16u * st, v[0][0], v[0][1], v[1][0], v[1][1], v[0][2], v[0][3], v[1][2], v[1][3]);
+                    tc_st_16x256b_x2(ta + (16u << 16) + 16u * st, v[2][0], v[2][1], v[3][0], v[3][1], v[2][2], v[2][3], v[3][2], v[3][3]);
+#endif
                 }
+                TS_PROF_END(1)
+                TS_PROF_BEGIN
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                TS_PROF_END(2)
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(a_full + 8 * ra.idx);
-                ra.advance(kTsASlots);
+                if (lane == 0) mbar_arrive(a_full + 8 * a_idx);
+                a_idx += 4;
+                if (a_idx >= A) { a_idx -= A; a_phase ^= 1u; }
             }
         }
+#ifdef TUNA_TS_PROFILE
+        pw_[3] = clock64() - loop_c0;
+#endif
     }
 
     // ------------------------------------------------------------------ common exit
+    TS_PROF_MARK(2)
     tc_fence_before();
     __syncthreads();
+    TS_PROF_MARK(3)
+    TS_PROF_STORE
     if (warp == 0) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTsTmemCols) : "memory");
@@ -456,7 +583,8 @@ int gemm_tstream_normalize_config(int m, int n, int k, int sm_count, tuna_config
     if (c->tile_tok == 0) c->tile_tok = (n <= 16) ? 16 : (n <= 32 ? 32 : 64);
     if (c->tile_tok != 16 && c->tile_tok != 32 && c->tile_tok != 64) return TUNA_ERR_BAD_CONFIG;
     if (c->row_blocks == 0) c->row_blocks = 1;
-    if (c->row_blocks < 1 || c->row_blocks * c->tile_tok > kTsAccCols) return TUNA_ERR_BAD_CONFIG;
+    if ((c->row_blocks != 1 && c->row_blocks != 2 && c->row_blocks != 4) || c->row_blocks * c->tile_tok > kTsAccCols)
+        return TUNA_ERR_BAD_CONFIG;
     if (c->ctas < 0) return TUNA_ERR_BAD_CONFIG;
     if (c->ctas == 0 || c->ctas > sm_count) c->ctas = sm_count;
     return TUNA_OK;
@@ -506,6 +634,10 @@ int launch_gemm_tstream(const GemmArgs &a, const tuna_config &c)
     p.q = a.q; p.x = (const __half *)a.x; p.code = a.code; p.absmax = a.absmax; p.o = (__half *)a.o;
     p.m = a.m; p.n = a.n; p.k = a.k;
     p.row_blocks = c.row_blocks;
+    p.acc_cols = c.row_blocks * c.tile_tok < 32 ? 32 : c.row_blocks * c.tile_tok;  // 32-column allocation granule
+    p.a_base = 2 * p.acc_cols;
+    p.a_slots = (kTsTmemCols - p.a_base) / kTsSlotCols;
+    if (p.a_slots > kTsMaxASlots) p.a_slots = kTsMaxASlots;
     p.chunks = div_up(a.k, kTsChunkK);
     p.row_tiles = div_up(a.m, kBlockRows * c.row_blocks);
     const long long units = (long long)p.row_tiles * p.chunks;
@@ -536,3 +668,11 @@ int launch_gemm_tstream(const GemmArgs &a, const tuna_config &c)
 }
 
 }  // namespace tuna
+
+#ifdef TUNA_TS_PROFILE
+extern "C" int tuna_debug_ts_profile(void *host_out, size_t bytes)
+{
+    if (bytes > sizeof(long long) * 160 * 24 * 8) bytes = sizeof(long long) * 160 * 24 * 8;
+    return (int)cudaMemcpyFromSymbol(host_out, g_ts_prof, bytes);
+}
+#endif

@@ -61,7 +61,8 @@ typedef struct tuna_config {
     int32_t rows_per_warp; /* stream: 32-row blocks per warp (1|2)                    */
     int32_t warps_m;       /* stream: consumer warps along output rows (power of 2)   */
     int32_t warps_k;       /* stream: consumer warps along K (power of 2, m*k <= 16)  */
-    int32_t k_steps;       /* stream: 32-column steps per warp per unit (8|16|32|64)  */
+    int32_t k_steps;       /* stream: 32-column steps per warp per unit (8|16|32|64); *
+                            * tstream: 32-column steps per slot (4|8)                 */
     int32_t ctas;          /* persistent CTAs (0 = one per SM)                        */
     int32_t stages_w;      /* umma: packed-weight ring depth (64-column stages)       */
     int32_t stages_x;      /* umma: unit stages (activation tile + A-operand slots)   */

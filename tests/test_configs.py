@@ -50,7 +50,10 @@ def test_render_field_order():
 def test_lookup_always_yields_a_runnable_config(tuna_lib, m, k, n):
     cfg = _lib.TunaConfig()
     assert tuna_lib.tuna_lookup_config(m, n, k, ctypes.byref(cfg)) == 0
-    assert cfg.path in (_lib.PATH_STREAM, _lib.PATH_UMMA)
+    assert cfg.path in (_lib.PATH_STREAM, _lib.PATH_UMMA, _lib.PATH_TSTREAM)
+    if cfg.path == _lib.PATH_TSTREAM:
+        assert cfg.tile_tok in (16, 32, 64) and cfg.row_blocks in (1, 2, 4) and cfg.k_steps in (4, 8)
+        assert cfg.row_blocks * cfg.tile_tok <= 64
     if cfg.path == _lib.PATH_STREAM:
         assert cfg.tile_tok in (8, 16, 32) and cfg.rows_per_warp in (1, 2)
         assert 1 <= cfg.warps_m * cfg.warps_k <= 16 and cfg.k_steps in (4, 8, 16, 32, 64)

@@ -44,24 +44,27 @@ def test_tstream_one_hot_activations_recover_the_weights():
     assert holder.guards_intact()
 
 
+@pytest.mark.parametrize("k_steps", [4, 8])
 @pytest.mark.parametrize("m,n,k", [(128, 16, 128), (128, 16, 256), (256, 16, 512), (512, 16, 1024), (1024, 16, 2048)])
-def test_tstream_single_tile_then_many(m, n, k):
-    _run(m, n, k, seed=m + k, tile_tok=16, row_blocks=1)
+def test_tstream_single_tile_then_many(m, n, k, k_steps):
+    _run(m, n, k, seed=m + k, tile_tok=16, row_blocks=1, k_steps=k_steps)
 
 
+@pytest.mark.parametrize("k_steps", [4, 8])
 @pytest.mark.parametrize("row_blocks", [1, 2, 4])
 @pytest.mark.parametrize("m,n,k", [(1024, 16, 1024), (136, 3, 72), (4104, 9, 520), (8, 1, 8)])
-def test_tstream_row_blocks_and_ragged_edges(m, n, k, row_blocks):
-    _run(m, n, k, seed=1, tile_tok=16, row_blocks=row_blocks)
+def test_tstream_row_blocks_and_ragged_edges(m, n, k, row_blocks, k_steps):
+    _run(m, n, k, seed=1, tile_tok=16, row_blocks=row_blocks, k_steps=k_steps)
 
 
+@pytest.mark.parametrize("k_steps", [4, 8])
 @pytest.mark.parametrize("ctas", [1, 3, 7, 148])
-def test_tstream_split_across_ctas_is_order_independent(ctas):
+def test_tstream_split_across_ctas_is_order_independent(ctas, k_steps):
     # few tiles, many CTAs: every tile is cut across CTAs and finished through the workspace
     m, n, k = 512, 16, 4096
     host, dev = make_case(m, n, k, 4)
     ref = orc.matmul_ref(*host, m, n, k)
-    cfg = _lib.TunaConfig(path=_lib.PATH_TSTREAM, tile_tok=16, row_blocks=1, ctas=ctas)
+    cfg = _lib.TunaConfig(path=_lib.PATH_TSTREAM, tile_tok=16, row_blocks=1, ctas=ctas, k_steps=k_steps)
     first = None
     for _ in range(5):
         out = torch.full((n, m), float("nan"), dtype=torch.float16, device="cuda")  # garbage on purpose
@@ -76,9 +79,10 @@ def test_tstream_split_across_ctas_is_order_independent(ctas):
             assert np.array_equal(first, got.view(np.uint16))
 
 
+@pytest.mark.parametrize("k_steps", [4, 8])
 @pytest.mark.parametrize("n,tile_tok,row_blocks", [(17, 32, 1), (32, 32, 2), (40, 16, 1), (64, 64, 1), (100, 64, 1), (33, 32, 2)])
-def test_tstream_token_tiles_and_passes(n, tile_tok, row_blocks):
-    _run(640, n, 520, seed=n, tile_tok=tile_tok, row_blocks=row_blocks)
+def test_tstream_token_tiles_and_passes(n, tile_tok, row_blocks, k_steps):
+    _run(640, n, 520, seed=n, tile_tok=tile_tok, row_blocks=row_blocks, k_steps=k_steps)
 
 
 @pytest.mark.parametrize("m,k", [(6144, 4096), (28672, 4096), (4096, 14336), (57344, 8192)])

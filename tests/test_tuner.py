@@ -7,7 +7,7 @@ from tuna_b200 import _lib, tuner
 
 def test_genomes_stay_inside_the_search_space():
     rng = random.Random(0)
-    for path in ("stream", "umma"):
+    for path in ("stream", "tstream", "umma"):
         space = tuner.space_for(path)
         g = tuner.random_genome(rng, path)
         for _ in range(50):
@@ -33,3 +33,20 @@ def test_config_fields_round_trip():
     cfg = tuner.to_config("umma", 64, dict(row_blocks=2, stages_w=6, stages_x=4, stages_a=8, dequant_warps=8, k_accs=2))
     d = cfg.as_dict()
     assert d["path"] == _lib.PATH_UMMA and d["tile_tok"] == 64 and d["row_blocks"] == 2 and d["k_accs"] == 2
+
+
+def test_path_is_part_of_the_search():
+    assert tuner.candidate_paths(16) == ("tstream", "stream")
+    assert "umma" in tuner.candidate_paths(64) and "tstream" in tuner.candidate_paths(64)
+    assert tuner.candidate_paths(2048) == ("umma",)
+    assert tuner.tile_tok_for("tstream", 9) == 16 and tuner.tile_tok_for("tstream", 40) == 64
+    assert tuner.tile_tok_for("stream", 8) == 8 and tuner.tile_tok_for("umma", 2048) == 256
+
+
+def test_tstream_validity(tuna_lib):
+    ok = tuner.to_config("tstream", 16, dict(row_blocks=2, k_steps=8))
+    assert tuner.is_valid(tuna_lib, 4096, 16, 4096, ok)
+    too_wide = tuner.to_config("tstream", 64, dict(row_blocks=2, k_steps=8))  # 2 x 64 accumulator columns > 64
+    assert not tuner.is_valid(tuna_lib, 4096, 64, 4096, too_wide)
+    bad_steps = tuner.to_config("tstream", 16, dict(row_blocks=1, k_steps=16))
+    assert not tuner.is_valid(tuna_lib, 4096, 16, 4096, bad_steps)

@@ -8,12 +8,12 @@
 // The idea.  The packed layout stores an 8x8 weight tile as 32 bytes in mma A-fragment order
 // (test.py:58-65: byte j = row j/4, column pair j%4).  A 16-byte piece of it is 4 rows x 8
 // columns, and that is exactly what one thread supplies to two tcgen05.st of shape 16x256b:
-// lane (g, t) of a warp (g = lane/4, t = lane%4) loads the 16 bytes of row group g/2, rows
-// 4(g%2)..+3, 8-column tile t of a 32-column step with ONE 128-bit ld.global (a warp load =
-// four fully used 128-byte lines), turns its 16 bytes into 16 half2 by 16 table lookups and
-// stores them into tensor memory with two instructions.  No shared-memory staging of the
-// weights, no shuffles, no transposition: the dequantised weights exist only in registers and
-// tensor memory.  The price is a permutation that costs nothing:
+// lane (g, t) of a warp (g = lane/4, t = lane%4) takes the 16 bytes of row group g/2, rows
+// 4(g%2)..+3, 8-column tile t of a 32-column step (one 128-bit shared load; a quarter-warp
+// reads 128 contiguous bytes), turns them into 16 half2 by 16 table lookups and stores them
+// into tensor memory with two instructions.  No shuffles, no transposition: the dequantised
+// weights exist only in registers and tensor memory.  The price is a permutation that costs
+// nothing:
 //   * rows: tensor-memory lane l of a 32-lane quarter holds weight row 4*(l%8) + l/8 of the
 //     quarter's 32 rows (undone by the epilogue, which owns one lane per thread);
 //   * K: column c of a step's 16 tensor-memory columns holds the column pair
@@ -22,22 +22,36 @@
 //     activation producer writes x into shared memory in the same order (8-byte pieces), which
 //     is free because it has to re-tile x into 8x16-byte core matrices anyway.
 //
-// One persistent CTA per SM, warp-specialised (24 warps, warps 2-3 idle; 80 registers per
+// The packed weights are staged by TMA: one 2-D box per slot (16 row groups x 512 or 1024 bytes
+// = 128 rows x 128 or 256 columns, the matrix viewed as [m/8] x [k] 32-bit words) into an
+// mbarrier-tracked ring that takes all the shared memory left (about 110 KB in flight per SM
+// whatever the consumers are doing), out-of-range rows and columns zero-filled by the copy engine.  (A first version streamed the weights with
+// ld.global into a per-lane register ring: 64 KB per SM at best, less whenever a warp was busy
+// converting, and the loaded HBM latency of ~2 us capped it near 3.3 TB/s.)
+//
+// One persistent CTA per SM, warp-specialised (24 warps; 80 registers per
 // thread.  Re-balancing registers between warpgroups with setmaxnreg made ptxas spill more,
 // not less, in this kernel):
-//   warp 0       MMA issue: tcgen05.mma (M=128, N=tile_tok, K=16, fp32 accumulate), A from
-//                tensor memory, B through a no-swizzle shared-memory descriptor, D in tensor memory
-//   warp 1       activation producer: x (fp16 [n,k], L2 resident) -> shared memory in
-//                core-matrix order with 8-byte cp.async, 128-column chunks, 6-deep ring
+//   warp 0       MMA issue: tcgen05.mma (M=128, N=tile_tok, K=16, fp32 accumulate), A from tensor
+//                memory, B through a no-swizzle shared-memory descriptor, D in tensor memory.
+//                The warp stays converged and one elected lane issues (a lone diverged thread
+//                running this loop needed ~80 clocks per MMA instead of ~12); a slot is 8 or 16
+//                MMAs per wait and commit, because that fixed cost per slot is what limits it
+//   warps 1, 3   activation re-tiling (alternating units): natural order -> the MMAs'
+//                core-matrix order with the K permutation above (128-bit shared loads, 64-bit
+//                shared stores)
+//   warp 2       copy producer: TMA boxes of packed weights into the weight ring and of x (fp16
+//                [n,k], L2 resident) into a natural-order activation ring
 //   warps 4-7    epilogue: tcgen05.ld of the accumulator, fp32 scale by absmax, fp16 store,
 //                split-K partials and fix-up
-//   warps 8-23   dequant: 128-bit ld.global.nc into an 8-deep register ring -> prmt + ld.shared
-//                table lookups -> tcgen05.st into the A slots.  Warp (quarter q, group j)
-//                handles rows 32q..+31 of the 128x128 slots j, j+4, j+8, ... of the CTA.
+//   warps 8-23   dequant: ld.shared.v4 -> prmt + ld.shared table lookups -> tcgen05.st into the A
+//                slots.  A warp handles rows 32q..+31 (q = its 32-lane quarter) and four
+//                32-column steps of a slot; with 128-column slots four groups of four warps
+//                convert four slots at once, with 256-column slots two groups of eight warps two.
 // The scale is constant along K (one block per row, test.py:81, kernel.cu:2178-2180) and is
 // applied once, in fp32, to the accumulated sum.
 //
-// Work decomposition ("stream-K"): a unit is (tile of 128*row_blocks rows, 128-column chunk) =
+// Work decomposition ("stream-K"): a unit is (tile of 128*row_blocks rows, 128- or 256-column chunk) =
 // row_blocks slots; the units, tile-major, are cut into one contiguous range per CTA so that
 // every SM streams the same number of bytes whatever the shape.  A tile cut across CTAs is
 // finished by whichever CTA arrives last at the tile's counter (per 32-row quarter): it adds
@@ -87,21 +101,19 @@ __device__ __forceinline__ long long ts_gtime()
 
 namespace tuna {
 
-constexpr int kTsChunkK = 128;        // K extent of a unit / an A slot
-constexpr int kTsSlotCols = 64;       // tensor-memory columns of one A slot (128 rows x 128 fp16)
-constexpr int kTsMaxASlots = 8;       // A-slot ring: as many as the accumulators leave room for (6 or 7)
-constexpr int kTsAccCols = 64;        // columns of one accumulator buffer (row_blocks * tile_tok <= 64)
+constexpr int kTsMaxASlots = 8;       // A-slot ring: as many slots as the accumulators leave room for
 constexpr int kTsTmemCols = 512;
 constexpr int kTsMaxXStages = 6;
-constexpr int kTsLoads = 8;           // 128-bit weight loads in flight per lane
-constexpr int kTsEpilogueWarp0 = 4;   // warps 2-3 idle: the epilogue warps' quarters are 0..3 in order
+constexpr int kTsMaxWStages = 16;     // weight ring: as many stages as shared memory holds
+constexpr int kTsLutBytes = 256 * 128;    // byte -> half2 table: 256 entries, 32 copies (one per bank) of 4 bytes
+constexpr int kTsSmemTotal = 227 * 1024;             // static + dynamic shared memory of a CTA on sm_100
+constexpr int kTsSmemDynamic = kTsSmemTotal - 1024;  // the static part (barriers) stays below 1 KB
+constexpr int kTsEpilogueWarp0 = 4;   // the epilogue warps' quarters are 0..3 in order
 constexpr int kTsDequantWarp0 = 8;
 constexpr int kTsDequantWarps = 16;
 constexpr int kTsThreads = 32 * (kTsDequantWarp0 + kTsDequantWarps);
 
 struct TsParams {
-    const uint8_t *q;
-    const __half *x;
     const float *code;
     const float *absmax;
     __half *o;
@@ -114,11 +126,22 @@ struct TsParams {
     int a_slots;      // A-slot ring depth
     int a_base;       // first tensor-memory column of the A slots (behind the two accumulator buffers)
     int acc_cols;     // columns of one accumulator buffer
-    int chunks;       // ceil(k / 128)
+    int chunks;       // ceil(k / chunk columns)
     int row_tiles;    // ceil(m / (128 RB))
     int units;        // row_tiles * chunks
     int units_q, units_r;  // units = units_q * CTAs + units_r: the first units_r CTAs take units_q + 1
 };
+
+// Table lookup: the selected byte of w (two 4-bit codes) -> half2 of the two code values.  Entry e
+// of the table lies at 128 * e, one copy per bank: conflict free.
+__device__ __forceinline__ uint32_t ts_lookup(uint32_t w, uint32_t lane_base, uint32_t selector)
+{
+    uint32_t b, v;
+    asm("prmt.b32 %0, %1, 0, %2;" : "=r"(b) : "r"(w), "r"(selector));
+    // not volatile: the table is constant once built, so the compiler may schedule lookups freely
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(lane_base + (b << 7)));
+    return v;
+}
 
 // The CTA whose range holds unit u.
 __device__ __forceinline__ int ts_cta_of_unit(const TsParams &p, int u)
@@ -127,16 +150,29 @@ __device__ __forceinline__ int ts_cta_of_unit(const TsParams &p, int u)
     return u < big ? u / (p.units_q + 1) : p.units_r + (u - big) / p.units_q;
 }
 
-template <int N_TILE>
-__global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const TsParams p)
+// STEPS: 32-column steps per slot (4 or 8).
+template <int N_TILE, int STEPS>
+__global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const TsParams p, const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_x)
 {
-    constexpr uint32_t kBTileBytes = N_TILE * 32;           // one 16-wide MMA's activations
-    constexpr uint32_t kXStageBytes = 8 * kBTileBytes;      // 4 steps x 2 MMAs
-    constexpr uint32_t kLbo = N_TILE * 16, kSbo = 128;
+    constexpr int kChunkK = 32 * STEPS;                     // columns of a unit / slot
+    constexpr int kSlotCols = 16 * STEPS;                   // tensor-memory columns of one A slot
+    constexpr int kSlotBytes = 16 * kChunkK * 4;            // packed bytes of a slot: 16 row groups x 4 bytes per column
+    constexpr int kHalves = STEPS / 4;                      // warps that share a quarter of a slot
+    constexpr int kGroups = kTsDequantWarps / (4 * kHalves);  // slots converted at once
+    // One 16-wide MMA's activations ("B tile"): [K half][token/8][token%8][16 bytes].  The K halves
+    // lie kLbo apart and consecutive tiles kBTile apart; both carry 32 bytes of padding so that the
+    // permuting warp's 8-byte stores of a half-warp (2 tokens x 8 weight tiles = 2 K halves x 2
+    // steps x ...) fall into 16 different 8-byte bank pairs.
+    constexpr uint32_t kLbo = N_TILE * 16 + 32, kSbo = 128;
+    constexpr uint32_t kBTile = 2 * kLbo + 32;
+    constexpr uint32_t kXStageBytes = 2 * STEPS * kBTile;             // permuted chunk, as the MMAs read it
+    constexpr uint32_t kXNatBytes = N_TILE * kChunkK * 2;             // chunk as TMA delivers it: [token][kChunkK] fp16
+    constexpr int kXN = N_TILE == 16 ? 4 : (N_TILE == 32 ? 3 : 2);    // natural-order stages (TMA -> permuting warp)
+    constexpr int kXS = N_TILE == 16 ? 3 : 2;                         // permuted stages (permuting warp -> MMA)
+    static_assert(kXN <= kTsMaxXStages && kXS <= kTsMaxXStages, "barrier arrays too small");
+    static_assert(kLbo % 16 == 0 && kBTile % 16 == 0 && (kLbo % 128) == 32 && ((2 * kBTile) % 128) == 64, "operand tile padding");
     extern __shared__ __align__(1024) uint8_t smem[];
-    constexpr int kXS = N_TILE == 64 ? 3 : 6;   // activation stages (48 KB at most)
-    constexpr int kLag = N_TILE == 64 ? 1 : 3;  // units between issuing a stage's copies and handing it over
-    __shared__ __align__(8) uint64_t bars[2 * kTsMaxASlots + 2 * kTsMaxXStages + 4];
+    __shared__ __align__(8) uint64_t bars[2 * kTsMaxASlots + 4 * kTsMaxXStages + 4 + 2 * kTsMaxWStages];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
@@ -148,15 +184,22 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     // Let the next kernel in the stream become resident as SMs free up.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // shared memory: the activation ring at the start of the dynamic window, the table at the
-    // first 64-KB boundary of the shared address space
-    const uint32_t xring = smem_u32(smem);
-    const uint32_t lut_addr = (xring + kXS * kXStageBytes + 0xFFFFu) & ~0xFFFFu;
+    // Shared memory: the byte -> half2 table (32 KB: 256 entries x 32 bank copies), the two
+    // activation rings, and weight stages in everything that is left.
+    const uint32_t dyn0 = smem_u32(smem);
+    const uint32_t lut_addr = dyn0;
+    const uint32_t xnat = lut_addr + kTsLutBytes;
+    const uint32_t xring = xnat + kXN * kXNatBytes;
+    const uint32_t w0 = (xring + kXS * kXStageBytes + 1023u) & ~1023u;
+    const int WS = min(kTsMaxWStages, (int)((dyn0 + kTsSmemDynamic - w0) / kSlotBytes));
+    auto w_stage = [&](int i) -> uint32_t { return w0 + (uint32_t)i * kSlotBytes; };
 
     const uint32_t bar0 = smem_u32(&bars[0]);
     const uint32_t a_full = bar0, a_empty = a_full + 8 * kTsMaxASlots;
-    const uint32_t x_full = a_empty + 8 * kTsMaxASlots, x_empty = x_full + 8 * kXS;
-    const uint32_t d_full = x_empty + 8 * kXS, d_empty = d_full + 16;
+    const uint32_t x_full = a_empty + 8 * kTsMaxASlots, x_empty = x_full + 8 * kTsMaxXStages;
+    const uint32_t d_full = x_empty + 8 * kTsMaxXStages, d_empty = d_full + 16;
+    const uint32_t w_full = d_empty + 16, w_empty = w_full + 8 * kTsMaxWStages;
+    const uint32_t xn_full = w_empty + 8 * kTsMaxWStages, xn_empty = xn_full + 8 * kTsMaxXStages;
     volatile int *abort_flag = &s_abort;
 
     // this CTA's contiguous range of units
@@ -166,9 +209,11 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int i = 0; i < kTsMaxASlots; ++i) { mbar_init(a_full + 8 * i, 4); mbar_init(a_empty + 8 * i, 1); }
-        for (int i = 0; i < kXS; ++i) { mbar_init(x_full + 8 * i, 1); mbar_init(x_empty + 8 * i, 1); }
+        for (int i = 0; i < kTsMaxASlots; ++i) { mbar_init(a_full + 8 * i, 4 * kHalves); mbar_init(a_empty + 8 * i, 1); }
+        for (int i = 0; i < kTsMaxXStages; ++i) { mbar_init(x_full + 8 * i, 1); mbar_init(x_empty + 8 * i, 1); }
+        for (int i = 0; i < kTsMaxXStages; ++i) { mbar_init(xn_full + 8 * i, 1); mbar_init(xn_empty + 8 * i, 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(d_full + 8 * i, 1); mbar_init(d_empty + 8 * i, 4); }
+        for (int i = 0; i < kTsMaxWStages; ++i) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, 4 * kHalves); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -177,22 +222,21 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    __syncthreads();  // barriers initialised: the weight producer may start
 
     const int quarter = warp & 3;          // the 32 tensor-memory lanes this warp may access
     const int total_slots = n_units * RB;
 
-    // Rest of the prologue, run by every warp inside its own role's branch (so that the dequant
-    // warps can have their first weight loads in flight across it without those registers being
-    // live in the other roles): the byte -> half2 table (even column = high nibble in the low
-    // half), one copy per bank - the codebook is a constant, so this runs before the
-    // dependency wait - then the wait, then the CTA barrier that publishes table, barriers and
-    // the tensor-memory base.
+    // Rest of the prologue, run by every warp inside its own role's branch: the byte -> half2
+    // table (even column = high nibble in the low half), one copy per bank - the codebook is a
+    // constant, so this runs before the dependency wait - then the wait, then the CTA barrier
+    // that publishes the table and the tensor-memory base.
     auto finish_prologue = [&]() -> uint32_t {
         const float cv = p.code[lane & 15];
         const uint32_t ch = (uint32_t)__half_as_ushort(__float2half_rn(cv));
         for (int e = warp; e < 256; e += kTsThreads / 32) {
             const uint32_t v = __shfl_sync(0xffffffffu, ch, e >> 4) | (__shfl_sync(0xffffffffu, ch, e & 15) << 16);
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(lut_addr + (uint32_t)e * 256 + lane * 4), "r"(v) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(lut_addr + (uint32_t)e * 128 + lane * 4), "r"(v) : "memory");
         }
         asm volatile("griddepcontrol.wait;" ::: "memory");
         tc_fence_before();
@@ -206,39 +250,43 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     if (warp == 0) {
         // ------------------------------------------------------------------ MMA issue
         // The warp stays converged: every lane runs the loop and the waits, one elected lane
-        // issues the MMAs and the commits.
+        // issues the MMAs and the commits.  Descriptors: the high word is constant, the low word
+        // is the operand address and the leading byte offset.
         tmem = finish_prologue();
         constexpr uint32_t idesc = make_idesc(N_TILE);
+        constexpr uint32_t desc_hi = (kSbo >> 4) | (1u << 14);
         Ring ra, rx, rd;
-        int tile = tile0, chunk = chunk0;
+        int chunk = chunk0;
         bool seg_first = true;  // first unit of a segment (the units of one tile inside the range)
-        for (int u = 0; u < n_units; ++u) {
+        bool ok = true;
+        for (int u = 0; ok && u < n_units; ++u) {
             const bool seg_last = (chunk + 1 == p.chunks) || (u + 1 == n_units);
-            bool ok = true;
             TS_PROF_BEGIN
             if (seg_first) ok = mbar_wait(d_empty + 8 * rd.idx, rd.phase ^ 1, abort_flag, p.status, 3);
             TS_PROF_END(0)
             TS_PROF_BEGIN
             ok = ok && mbar_wait(x_full + 8 * rx.idx, rx.phase, abort_flag, p.status, 4);
-            if (!__all_sync(0xffffffffu, ok)) break;
+            ok = __all_sync(0xffffffffu, ok) != 0;
             TS_PROF_END(1)
-            const uint32_t xbase = xring + (uint32_t)rx.idx * kXStageBytes;
+            if (!ok) break;
+            const uint32_t desc_lo0 = (((xring + (uint32_t)rx.idx * kXStageBytes) & 0x3FFFFu) >> 4) | ((kLbo >> 4) << 16);
             const uint32_t dbase = tmem + (uint32_t)(rd.idx * p.acc_cols);
             for (int rb = 0; rb < RB; ++rb) {
                 TS_PROF_BEGIN
-                if (!mbar_wait_warp(a_full + 8 * ra.idx, ra.phase, abort_flag, p.status, 5)) { ok = false; break; }
+                ok = mbar_wait_warp(a_full + 8 * ra.idx, ra.phase, abort_flag, p.status, 5);
                 TS_PROF_END(2)
+                if (!ok) break;
                 tc_fence_after();
                 TS_PROF_BEGIN
                 if (elect_one_sync()) {
-                    const uint32_t abase = tmem + (uint32_t)p.a_base + (uint32_t)ra.idx * kTsSlotCols;
+                    const uint32_t abase = tmem + (uint32_t)p.a_base + (uint32_t)ra.idx * kSlotCols;
 #pragma unroll
 #ifdef TS_ABL_NOMMA  // timing experiment: commits only
                     for (int mm = 0; mm < 0; ++mm) {
 #else
-                    for (int mm = 0; mm < 8; ++mm) {  // step mm/2, 16-wide MMA mm%2
+                    for (int mm = 0; mm < 2 * STEPS; ++mm) {  // step mm/2, 16-wide MMA mm%2
 #endif
-                        const uint64_t bdesc = make_desc_noswizzle(xbase + mm * kBTileBytes, kLbo, kSbo);
+                        const uint64_t bdesc = ((uint64_t)desc_hi << 32) | (uint64_t)(desc_lo0 + mm * (kBTile >> 4));
                         tc_mma_ts(dbase + (uint32_t)rb * N_TILE, abase + mm * 8, bdesc, idesc, (seg_first && mm == 0) ? 0u : 1u);
                     }
                     tc_commit(a_empty + 8 * ra.idx);
@@ -251,95 +299,122 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
                 TS_PROF_END(3)
                 ra.advance(p.a_slots);
             }
-            if (!ok) break;
             rx.advance(kXS);
             if (seg_last) rd.advance(2);
             seg_first = seg_last;
-            if (++chunk == p.chunks) { chunk = 0; ++tile; }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ activation producer
-        // 8-byte cp.async copies (no registers, many in flight), issued kLag units ahead of the
-        // unit that is handed to the MMA warp.  Lane (tok%8 = lane%8, t%2 = (lane/8)%2, lane/16)
-        // so that a half-warp writes one 128-byte core matrix (8 tokens x 16 bytes), conflict
-        // free; copy i of a unit covers rest = 2*(i/2) + lane/16 over (t/2 [2], step [4],
-        // tok/8 [N_TILE/8]) and MMA u = i%2.
-        tmem = finish_prologue();
-        Ring rx, rdone;
-        int chunk = chunk0;
-        const int tok_lo = lane & 7, t_lo = (lane >> 3) & 1, rest_lo = lane >> 4;
-        // per copy i: source offset in halfs relative to x[tok0][k0] (-1: token past n), its
-        // column inside the chunk, and the destination offset inside a stage - all independent of
-        // the unit.  Kept in registers for the 16-token tile (whose units are the shortest).
-        const __half *x_pass = p.x + (size_t)p.tok0 * p.k;
-        auto copy_params = [&](int i, int &src_off, int &col, uint32_t &dst) {
-            const int rest = (i & ~1) + rest_lo, uu = i & 1;
-            const int t_hi = rest & 1, step = (rest >> 1) & 3, ng = rest >> 3;
-            const int tok = ng * 8 + tok_lo;
-            col = 32 * step + 8 * (2 * t_hi + t_lo);
-            src_off = p.tok0 + tok < p.n ? tok * p.k + col + 4 * uu : -1;
-            // B tile (step, u): [t/2][tok/8][tok%8][16 bytes]; columns col + 4u .. +3 of the
-            // 8-column weight tile go to MMA u, at byte 8*(t%2) of the token's row
-            dst = (uint32_t)(2 * step + uu) * kBTileBytes + (uint32_t)t_hi * kLbo + (uint32_t)ng * kSbo + (uint32_t)tok_lo * 16 + (uint32_t)t_lo * 8;
-        };
-        constexpr bool kHoist = N_TILE == 16;
-        int src_off[kHoist ? N_TILE : 1], col_off[kHoist ? N_TILE : 1];
-        uint32_t dst_off[kHoist ? N_TILE : 1];
-        if (kHoist) {
-#pragma unroll
-            for (int i = 0; i < N_TILE; ++i) copy_params(i, src_off[i], col_off[i], dst_off[i]);
-        }
-        auto hand_over = [&]() {
-            // this lane's copies of the oldest unit have landed; generic-proxy writes -> visible
-            // to the tensor core's (async proxy) reads; then one arrival for the warp
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(x_full + 8 * rdone.idx);
-            rdone.advance(kXS);
-        };
-        bool ok = true;
-        for (int u = 0; u < n_units; ++u) {
-            TS_PROF_BEGIN
-            if (!mbar_wait_warp(x_empty + 8 * rx.idx, rx.phase ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
-            TS_PROF_END(0)
-            const uint32_t stage = xring + (uint32_t)rx.idx * kXStageBytes;
-            const int k0 = chunk * kTsChunkK;
-            const __half *xk = x_pass + k0;
-            auto copy_one = [&](int so, int co, uint32_t dd) {
-                const bool in = so >= 0 && k0 + co < p.k;
-                const __half *src = in ? xk + so : p.x;
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(stage + dd), "l"(src), "r"(in ? 8u : 0u) : "memory");
-            };
-            if constexpr (kHoist) {
-#pragma unroll
-                for (int i = 0; i < N_TILE; ++i) copy_one(src_off[i], col_off[i], dst_off[i]);
-            } else {
-#pragma unroll 8
-                for (int i = 0; i < N_TILE; ++i) {
-                    int so, co;
-                    uint32_t dd;
-                    copy_params(i, so, co, dd);
-                    copy_one(so, co, dd);
-                }
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            if (u >= kLag) {
-                TS_PROF_BEGIN
-                asm volatile("cp.async.wait_group %0;" ::"n"(kLag) : "memory");
-                TS_PROF_END(1)
-                hand_over();
-            }
-            rx.advance(kXS);
             if (++chunk == p.chunks) chunk = 0;
         }
-        if (ok) {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            for (int u = max(n_units - kLag, 0); u < n_units; ++u) hand_over();
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else if (warp == 1 || warp == 3) {
+        // ------------------------------------------------------------------ activation re-tiling
+        // Two warps, alternating units.  Natural order ([token][column], as TMA delivers it) -> the
+        // MMAs' order: per step two operand tiles (u = 0, 1) of [K half][token/8][token%8][16 bytes],
+        // the 16 bytes of a token being the 8-byte column groups 4u .. 4u+3 of the 8-column weight
+        // tiles 2(K half), 2(K half)+1 of the step.  A lane moves one token's 16 bytes of one
+        // weight tile per trip: one 128-bit shared load (a quarter-warp reads 128 contiguous
+        // bytes), two 64-bit shared stores (conflict free thanks to the padding of kLbo and
+        // kBTile).  This costs the load/store unit a quarter of what the unit's table lookups
+        // cost; an earlier version that re-tiled straight from global memory with 8-byte cp.async
+        // cost as much as the lookups.
+        tmem = finish_prologue();
+        const int me = warp >> 1;  // 0 or 1: takes the units me, me + 2, ...
+        int n_idx = me % kXN, x_idx = me % kXS;  // ring positions of unit u: u % kXN, u % kXS
+        uint32_t n_phase = 0, x_phase = 0;
+        const int tokq = lane >> 3, tt8 = lane & 7;
+        const uint32_t src_lane = (uint32_t)tokq * (kChunkK * 2) + (uint32_t)tt8 * 16;
+        const uint32_t dst_lane = (uint32_t)(2 * (tt8 >> 2)) * kBTile + (uint32_t)((tt8 >> 1) & 1) * kLbo + (uint32_t)(tt8 & 1) * 8 +
+                                  (uint32_t)(tokq & 1) * 16;  // + (token / 2 % 4) * 32 + (token / 8) * kSbo per trip
+        for (int u = me; u < n_units; u += 2) {
+            TS_PROF_BEGIN
+            bool ok = mbar_wait_warp(xn_full + 8 * n_idx, n_phase, abort_flag, p.status, 10);
+            ok = ok && mbar_wait_warp(x_empty + 8 * x_idx, x_phase ^ 1, abort_flag, p.status, 2);
+            TS_PROF_END(0)
+            if (!ok) break;
+            const uint32_t src0 = xnat + (uint32_t)n_idx * kXNatBytes + src_lane;
+            const uint32_t dst0 = xring + (uint32_t)x_idx * kXStageBytes + dst_lane;
+            // trips (tg, j): token 4 tg + tokq, weight tiles 8 j + tt8 (steps 2j, 2j+1); eight loads
+            // in flight, then their sixteen stores
+            constexpr int kTrips = (N_TILE / 4) * (STEPS / 2);
+#pragma unroll
+            for (int b0 = 0; b0 < kTrips; b0 += 8) {
+                uint4 v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int tg = (b0 + i) / (STEPS / 2), j = (b0 + i) % (STEPS / 2);
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[i].x), "=r"(v[i].y), "=r"(v[i].z), "=r"(v[i].w) : "r"(src0 + (uint32_t)(4 * tg) * (kChunkK * 2) + (uint32_t)j * 128));
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int tg = (b0 + i) / (STEPS / 2), j = (b0 + i) % (STEPS / 2);
+                    // token 4 tg + tokq: row (4 tg + tokq) % 8 of 8-token group (4 tg + tokq) / 8
+                    const uint32_t d = dst0 + (uint32_t)(4 * j) * kBTile + (uint32_t)(tg >> 1) * kSbo + (uint32_t)((4 * tg) & 7) * 16 + (uint32_t)(tokq >> 1) * 32;
+                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(d), "r"(v[i].x), "r"(v[i].y) : "memory");
+                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(d + kBTile), "r"(v[i].z), "r"(v[i].w) : "memory");
+                }
+            }
+            // generic-proxy writes -> visible to the tensor core's (async proxy) reads; the natural
+            // stage goes back to the copy warp (the arrival is a release, ordered after the loads)
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(x_full + 8 * x_idx);
+                mbar_arrive(xn_empty + 8 * n_idx);
+            }
+            n_idx += 2;
+            while (n_idx >= kXN) { n_idx -= kXN; n_phase ^= 1u; }
+            x_idx += 2;
+            while (x_idx >= kXS) { x_idx -= kXS; x_phase ^= 1u; }
         }
-    } else if (warp < kTsEpilogueWarp0) {
-        tmem = finish_prologue();  // idle warps
+    } else if (warp == 2) {
+        // ------------------------------------------------------------------ copy producer
+        // One elected lane of the converged warp issues every TMA copy of the CTA: a box per slot
+        // (16 row groups x kChunkK 32-bit words of packed weights) into the weight ring, and a box
+        // per unit (tile_tok tokens x kChunkK columns of x, L2 resident; tokens past n and columns
+        // past k zero-filled) into the natural-order activation ring.  The weights are constants:
+        // the first ring-full of their copies is issued before the dependency wait (and before
+        // this warp joins the rest of the prologue); x may come from the kernel before this one.
+        Ring rw, rn;
+        int sl = 0, w_tile = tile0, w_chunk = chunk0, w_rb = 0;
+        int xu = 0, x_chunk = chunk0;
+        bool ok = true;
+        auto issue_x = [&](bool blocking) {
+            // as many activation copies as have a free stage (all the outstanding ones if `blocking`)
+            while (ok && xu < n_units) {
+                if (blocking) ok = mbar_wait_warp(xn_empty + 8 * rn.idx, rn.phase ^ 1, abort_flag, p.status, 9);
+                else if (!(__all_sync(0xffffffffu, mbar_test_wait(xn_empty + 8 * rn.idx, rn.phase ^ 1)) != 0)) break;
+                if (!ok) break;
+                if (elect_one_sync()) {
+                    mbar_expect_tx(xn_full + 8 * rn.idx, kXNatBytes);
+                    tma_load_2d(xnat + (uint32_t)rn.idx * kXNatBytes, &tmap_x, x_chunk * kChunkK, p.tok0, xn_full + 8 * rn.idx);
+                }
+                __syncwarp();
+                rn.advance(kXN);
+                ++xu;
+                if (++x_chunk == p.chunks) x_chunk = 0;
+            }
+        };
+        auto issue_w_until = [&](int end, bool with_x) {
+            for (; ok && sl < end; ++sl) {
+                if (with_x) issue_x(false);
+                TS_PROF_BEGIN
+                ok = mbar_wait_warp(w_empty + 8 * rw.idx, rw.phase ^ 1, abort_flag, p.status, 1);
+                TS_PROF_END(0)
+                if (!ok) break;
+                if (elect_one_sync()) {
+                    mbar_expect_tx(w_full + 8 * rw.idx, kSlotBytes);
+                    tma_load_2d(w_stage(rw.idx), &tmap_q, w_chunk * kChunkK, (w_tile * RB + w_rb) * 16, w_full + 8 * rw.idx);
+                }
+                __syncwarp();
+                rw.advance(WS);
+                if (++w_rb == RB) {
+                    w_rb = 0;
+                    if (++w_chunk == p.chunks) { w_chunk = 0; ++w_tile; }
+                }
+            }
+        };
+        issue_w_until(min(WS, total_slots), false);
+        tmem = finish_prologue();
+        issue_w_until(total_slots, true);
+        issue_x(true);
     } else if (warp < kTsDequantWarp0) {
         // ------------------------------------------------------------------ epilogue
         tmem = finish_prologue();
@@ -451,110 +526,94 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         }
     } else {
         // ------------------------------------------------------------------ dequant
-        // Group j (4 warps, one per 32-lane quarter) converts the slots j, j+4, j+8, ... of this CTA
-        // whole: 4 steps = 4 loads per lane per slot, one wait / fence / arrival per slot.  The four
-        // groups work on four different slots at once, so the latency of a slot's chain (lookups ->
-        // tcgen05.st -> wait::st -> arrive) is overlapped four times.
-        // Position and first loads before anything else (the weights are constants; nothing another
-        // kernel writes is touched before griddepcontrol.wait).
-        const int group = (warp - kTsDequantWarp0) >> 2;
+        // A group (4 * kHalves warps: one per 32-lane quarter and per four steps of a slot) converts
+        // the slots j, j + kGroups, ... of this CTA: one wait / fence / arrival per slot and warp.
+        // The groups work on different slots at once, so the latency of a slot's chain (shared
+        // loads -> lookups -> tcgen05.st -> wait::st -> arrive) is overlapped kGroups times.
+        const int dq = warp - kTsDequantWarp0;
+        const int half = (dq >> 2) % kHalves;      // which four steps of the slot
+        const int group = dq / (4 * kHalves);
         const int g = lane >> 2, t = lane & 3;
-        const int n_rg = p.m >> 3;
-        const size_t rg_bytes = row_group_bytes(p.k);
-        const int A = p.a_slots;
-        // Cursor of the next slot to prefetch.  The group's slots are 4 apart in the CTA's slot
-        // sequence: with RB in {1, 2, 4} that is always the same row block of the tile
-        // (rb = group % RB) and 4 / RB units further on - no division in the loop.
-        const int rb = group % RB, ustep = 4 / RB;
-        int pf_unit = group / RB;
-        int pf_tile = (u_begin + pf_unit) / p.chunks, pf_chunk = (u_begin + pf_unit) - pf_tile * p.chunks;
-        const int lane_rg = 4 * quarter + (g >> 1);
-        const uint32_t lane_off = (uint32_t)(8 * t) * 4 + (g & 1) * 16;
-        // source and predicate mask (bit st = step st) of this lane's 4 loads of the slot at the
-        // cursor; advances the cursor
-        auto prefetch_prepare = [&](unsigned &mask) -> const uint8_t * {
-            const int rg = (pf_tile * RB + rb) * 16 + lane_rg;
-            const int col = pf_chunk * kTsChunkK + 8 * t;
-            const int steps_in = min((p.k - col + 31) >> 5, 4);  // steps whose 8-column tile starts before k
-            const bool in = pf_unit < n_units && rg < n_rg;
-            mask = in ? (1u << steps_in) - 1u : 0u;
-            const uint8_t *src = p.q + (in ? (size_t)rg * rg_bytes + (size_t)pf_chunk * (kTsChunkK * 4) + lane_off : 0);
-            pf_unit += ustep;
-            pf_chunk += ustep;
-            while (pf_chunk >= p.chunks) { pf_chunk -= p.chunks; ++pf_tile; }
-            return src;
-        };
-        uint4 ring[2][4];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            unsigned mask;
-            const uint8_t *src = prefetch_prepare(mask);
-#pragma unroll
-            for (int st = 0; st < 4; ++st) ring[h][st] = ldg_stream_pred(src + (mask ? st * 128 : 0), (mask >> st) & 1u);
-        }
         tmem = finish_prologue();
-        const uint32_t lane_key = (lut_addr & 0xFFFF0000u) | (uint32_t)(lane * 4);
-        const uint32_t a_lane0 = tmem + ((uint32_t)(32 * quarter) << 16) + (uint32_t)p.a_base;
-        int a_idx = group;      // ring position of slot `sl`: sl % A, parity of its use (sl / A) & 1
-        uint32_t a_phase = 0;
+        const uint32_t lane_key = lut_addr + (uint32_t)(lane * 4);  // this lane's copy of the table
+        const uint32_t a_lane0 = tmem + ((uint32_t)(32 * quarter) << 16) + (uint32_t)p.a_base + 64u * (uint32_t)half;
+        // this lane's 16 bytes of its first step inside a stage: row group 4*quarter + g/2 (a row
+        // group is kChunkK*4 bytes), step 4*half (128 bytes per step), tile t, row half g%2
+        const uint32_t lane_soff = (uint32_t)(4 * quarter + (g >> 1)) * (uint32_t)(kChunkK * 4) + (uint32_t)half * 512u + (uint32_t)t * 32u + (uint32_t)(g & 1) * 16u;
+        const int A = p.a_slots;
+        int a_idx = group % A, w_idx = group % WS;  // ring positions of slot `sl`: sl % A, sl % WS
+        uint32_t a_phase = (uint32_t)(group / A) & 1u, w_phase = (uint32_t)(group / WS) & 1u;
         bool ok = true;
 #ifdef TUNA_TS_PROFILE
         const long long loop_c0 = clock64();
 #endif
-        for (int sl = group; ok && sl < total_slots; sl += 8) {
+        for (int sl = group; ok && sl < total_slots; sl += kGroups) {
+            TS_PROF_BEGIN
+            ok = mbar_wait_warp(w_full + 8 * w_idx, w_phase, abort_flag, p.status, 8);
+            TS_PROF_END(3)
+            if (!ok) break;
+            uint4 wv[4];
+            {
+                const uint32_t src = w_stage(w_idx) + lane_soff;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                if (sl + 4 * h >= total_slots) break;
-                TS_PROF_BEGIN
-                if (!mbar_wait_warp(a_empty + 8 * a_idx, a_phase ^ 1, abort_flag, p.status, 7)) { ok = false; break; }
-                TS_PROF_END(0)
-                tc_fence_after();
-                TS_PROF_BEGIN
-                const uint32_t ta = a_lane0 + (uint32_t)a_idx * kTsSlotCols;
-                unsigned pf_mask;
-                const uint8_t *pf_src = prefetch_prepare(pf_mask);  // the slot two ahead of this one
+                for (int st = 0; st < 4; ++st)
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(wv[st].x), "=r"(wv[st].y), "=r"(wv[st].z), "=r"(wv[st].w) : "r"(src + st * 128));
+            }
+            // software pipeline: the 16 lookups of step st + 1 are in flight while step st is stored
+            uint32_t v[2][4][4];
+            auto lookups = [&](const uint4 &wq, uint32_t (&o)[4][4]) {
+                const uint32_t w[4] = {wq.x, wq.y, wq.z, wq.w};  // word r = row 4(g%2)+r, byte c = column pair c
 #pragma unroll
-                for (int st = 0; st < 4; ++st) {
-                    const uint4 wv = ring[h][st];
-#ifndef TS_ABL_NOLDG
-                    ring[h][st] = ldg_stream_pred(pf_src + (pf_mask ? st * 128 : 0), (pf_mask >> st) & 1u);
-#else
-                    ring[h][st].x += (uint32_t)(size_t)pf_src;  // timing experiment: no global loads
-#endif
-                    const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};  // word r = row 4(g%2)+r, byte c = column pair c
-                    uint32_t v[4][4];  // the step's 16 lookups in flight together
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
+                for (int r = 0; r < 4; ++r) {
 #ifdef TS_ABL_NOLUT  // timing experiment: no table lookups
-                        v[r][0] = w[r]; v[r][1] = w[r] + lane_key; v[r][2] = w[r] ^ lane_key; v[r][3] = w[r] >> 1;
+                    o[r][0] = w[r]; o[r][1] = w[r] + lane_key; o[r][2] = w[r] ^ lane_key; o[r][3] = w[r] >> 1;
 #else
-                        v[r][0] = lut_lookup(w[r], lane_key, 0x7604);
-                        v[r][1] = lut_lookup(w[r], lane_key, 0x7614);
-                        v[r][2] = lut_lookup(w[r], lane_key, 0x7624);
-                        v[r][3] = lut_lookup(w[r], lane_key, 0x7634);
-#endif
-                    }
-                    // rows 0, 1 -> lanes g, g+8; rows 2, 3 -> lanes g+16, g+24
-#ifdef TS_ABL_NOST  // timing experiment: keep the lookups alive, skip the stores
-                    asm volatile("" ::"r"(v[0][0] ^ v[0][1] ^ v[0][2] ^ v[0][3] ^ v[1][0] ^ v[1][1] ^ v[1][2] ^ v[1][3] ^ v[2][0] ^ v[2][1] ^ v[2][2] ^ v[2][3] ^ v[3][0] ^ v[3][1] ^ v[3][2] ^ v[3][3]), "r"(ta));
-#else
-                    tc_st_16x256b_x2(ta + 16u * st, v[0][0], v[0][1], v[1][0], v[1][1], v[0][2], v[0][3], v[1][2], v[1][3]);
-                    tc_st_16x256b_x2(ta + (16u << 16) + 16u * st, v[2][0], v[2][1], v[3][0], v[3][1], v[2][2], v[2][3], v[3][2], v[3][3]);
+                    o[r][0] = ts_lookup(w[r], lane_key, 0x4440);
+                    o[r][1] = ts_lookup(w[r], lane_key, 0x4441);
+                    o[r][2] = ts_lookup(w[r], lane_key, 0x4442);
+                    o[r][3] = ts_lookup(w[r], lane_key, 0x4443);
 #endif
                 }
-                TS_PROF_END(1)
-                TS_PROF_BEGIN
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                TS_PROF_END(2)
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(a_full + 8 * a_idx);
-                a_idx += 4;
-                if (a_idx >= A) { a_idx -= A; a_phase ^= 1u; }
+            };
+            lookups(wv[0], v[0]);
+            // All four shared loads of the stage have been issued and the first has returned (its
+            // data fed the lookups; they return in order): hand the stage back to the producer.  The
+            // arrival is a release: it is ordered after this warp's loads.
+            __syncwarp();
+            if (lane == 0) mbar_arrive(w_empty + 8 * w_idx);
+            TS_PROF_BEGIN
+            ok = mbar_wait_warp(a_empty + 8 * a_idx, a_phase ^ 1, abort_flag, p.status, 7);
+            TS_PROF_END(0)
+            if (!ok) break;
+            tc_fence_after();
+            TS_PROF_BEGIN
+            const uint32_t ta = a_lane0 + (uint32_t)a_idx * kSlotCols;
+#pragma unroll
+            for (int st = 0; st < 4; ++st) {
+                if (st < 3) lookups(wv[st + 1], v[(st + 1) & 1]);
+                uint32_t (&c)[4][4] = v[st & 1];
+                // rows 0, 1 -> lanes g, g+8; rows 2, 3 -> lanes g+16, g+24
+#ifdef TS_ABL_NOST  // timing experiment: keep the lookups alive, skip the stores
+                asm volatile("" ::"r"(c[0][0] ^ c[0][1] ^ c[0][2] ^ c[0][3] ^ c[1][0] ^ c[1][1] ^ c[1][2] ^ c[1][3] ^ c[2][0] ^ c[2][1] ^ c[2][2] ^ c[2][3] ^ c[3][0] ^ c[3][1] ^ c[3][2] ^ c[3][3]), "r"(ta));
+#else
+                tc_st_16x256b_x2(ta + 16u * st, c[0][0], c[0][1], c[1][0], c[1][1], c[0][2], c[0][3], c[1][2], c[1][3]);
+                tc_st_16x256b_x2(ta + (16u << 16) + 16u * st, c[2][0], c[2][1], c[3][0], c[3][1], c[2][2], c[2][3], c[3][2], c[3][3]);
+#endif
             }
+            TS_PROF_END(1)
+            TS_PROF_BEGIN
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            TS_PROF_END(2)
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a_full + 8 * a_idx);
+            a_idx += kGroups;
+            while (a_idx >= A) { a_idx -= A; a_phase ^= 1u; }
+            w_idx += kGroups;
+            while (w_idx >= WS) { w_idx -= WS; w_phase ^= 1u; }
         }
 #ifdef TUNA_TS_PROFILE
-        pw_[3] = clock64() - loop_c0;
+        pg_[3] = clock64() - loop_c0;
 #endif
     }
 
@@ -562,7 +621,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     TS_PROF_MARK(2)
     tc_fence_before();
     __syncthreads();
-    TS_PROF_MARK(3)
+    if (warp < kTsDequantWarp0) { TS_PROF_MARK(3) }
     TS_PROF_STORE
     if (warp == 0) {
         tc_fence_after();
@@ -572,21 +631,26 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
 
 // ------------------------------------------------------------------ host side
 
-// Dynamic shared memory: the activation ring, slack up to the next 64-KB boundary of the shared
-// window, the table.  The static part (barriers) sits in front of the dynamic window, so the
-// ring ends below 64 KB as long as it is smaller than 64 KB minus the static part.
-static size_t ts_smem_bytes() { return 65536 + kLut64Bytes; }
+// Columns of a slot: 256 (16 MMAs per wait and commit of the issuing warp) when the matrix is
+// large enough for 16-KB units to balance across the SMs, else 128.
+static int ts_steps(const tuna_config &c) { return c.k_steps == 4 ? 4 : 8; }
 
 int gemm_tstream_normalize_config(int m, int n, int k, int sm_count, tuna_config *c)
 {
-    (void)m; (void)k;
     if (c->tile_tok == 0) c->tile_tok = (n <= 16) ? 16 : (n <= 32 ? 32 : 64);
     if (c->tile_tok != 16 && c->tile_tok != 32 && c->tile_tok != 64) return TUNA_ERR_BAD_CONFIG;
-    if (c->row_blocks == 0) c->row_blocks = 1;
-    if ((c->row_blocks != 1 && c->row_blocks != 2 && c->row_blocks != 4) || c->row_blocks * c->tile_tok > kTsAccCols)
+    // two row blocks share an activation stage when the matrix is tall enough for 32-KB units to balance
+    if (c->row_blocks == 0) c->row_blocks = (m >= 8192 && c->tile_tok <= 32) ? 2 : 1;
+    if ((c->row_blocks != 1 && c->row_blocks != 2 && c->row_blocks != 4) || c->row_blocks * c->tile_tok > 64)
         return TUNA_ERR_BAD_CONFIG;
     if (c->ctas < 0) return TUNA_ERR_BAD_CONFIG;
     if (c->ctas == 0 || c->ctas > sm_count) c->ctas = sm_count;
+    if (c->k_steps == 0) {
+        // 256-column slots unless they leave fewer than ~12 units per CTA to balance with
+        const long long units256 = (long long)div_up(m, kBlockRows * c->row_blocks) * div_up(k, 256);
+        c->k_steps = units256 >= 12ll * c->ctas ? 8 : 4;
+    }
+    if (c->k_steps != 4 && c->k_steps != 8) return TUNA_ERR_BAD_CONFIG;
     return TUNA_OK;
 }
 
@@ -598,8 +662,8 @@ size_t gemm_tstream_workspace_bytes(int m, int n, int k, const tuna_config &c, i
     return partial_region_bytes(sm_count) + counters;
 }
 
-template <int N_TILE>
-static int launch_ts(const TsParams &p, int ctas, cudaStream_t stream)
+template <int N_TILE, int STEPS>
+static int launch_ts(const TsParams &p, const CUtensorMap &mq, const CUtensorMap &mx, int ctas, cudaStream_t stream)
 {
     static bool attr_set[64] = {false};  // one-time, per device, opt-in to large dynamic shared memory
     static std::mutex mu;
@@ -608,8 +672,8 @@ static int launch_ts(const TsParams &p, int ctas, cudaStream_t stream)
     {
         std::lock_guard<std::mutex> lock(mu);
         if (!attr_set[dev]) {
-            if (cudaFuncSetAttribute(gemm_w4a16_tstream_kernel<N_TILE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)ts_smem_bytes()) != cudaSuccess)
+            if (cudaFuncSetAttribute(gemm_w4a16_tstream_kernel<N_TILE, STEPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kTsSmemDynamic) != cudaSuccess)
                 return TUNA_ERR_NO_DEVICE;
             attr_set[dev] = true;
         }
@@ -617,28 +681,29 @@ static int launch_ts(const TsParams &p, int ctas, cudaStream_t stream)
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3((unsigned)ctas);
     lc.blockDim = dim3(kTsThreads);
-    lc.dynamicSmemBytes = ts_smem_bytes();
+    lc.dynamicSmemBytes = kTsSmemDynamic;
     lc.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    return cudaLaunchKernelEx(&lc, gemm_w4a16_tstream_kernel<N_TILE>, p) == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
+    return cudaLaunchKernelEx(&lc, gemm_w4a16_tstream_kernel<N_TILE, STEPS>, p, mq, mx) == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
 }
 
 int launch_gemm_tstream(const GemmArgs &a, const tuna_config &c)
 {
+    const int steps = ts_steps(c), chunk_k = 32 * steps, slot_cols = 16 * steps;
     TsParams p;
     std::memset(&p, 0, sizeof(p));
-    p.q = a.q; p.x = (const __half *)a.x; p.code = a.code; p.absmax = a.absmax; p.o = (__half *)a.o;
+    p.code = a.code; p.absmax = a.absmax; p.o = (__half *)a.o;
     p.m = a.m; p.n = a.n; p.k = a.k;
     p.row_blocks = c.row_blocks;
     p.acc_cols = c.row_blocks * c.tile_tok < 32 ? 32 : c.row_blocks * c.tile_tok;  // 32-column allocation granule
     p.a_base = 2 * p.acc_cols;
-    p.a_slots = (kTsTmemCols - p.a_base) / kTsSlotCols;
+    p.a_slots = (kTsTmemCols - p.a_base) / slot_cols;
     if (p.a_slots > kTsMaxASlots) p.a_slots = kTsMaxASlots;
-    p.chunks = div_up(a.k, kTsChunkK);
+    p.chunks = div_up(a.k, chunk_k);
     p.row_tiles = div_up(a.m, kBlockRows * c.row_blocks);
     const long long units = (long long)p.row_tiles * p.chunks;
     if (units >= (1ll << 30)) return TUNA_ERR_TOO_LARGE;
@@ -653,13 +718,27 @@ int launch_gemm_tstream(const GemmArgs &a, const tuna_config &c)
     if (ctas > p.units) ctas = p.units;
     p.units_q = p.units / ctas;
     p.units_r = p.units % ctas;
+    // packed weights as [m/8 row groups] x [k 32-bit words] (a row group is 4k bytes); box = one slot:
+    // 16 row groups x chunk_k words.  Rows and columns past the matrix are zero-filled by the copy.
+    CUtensorMap mq;
+    if (!make_tensor_map_2d(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.q, (uint64_t)a.k, (uint64_t)a.m / 8, (uint64_t)a.k * 4,
+                            (uint32_t)chunk_k, 16, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return TUNA_ERR_NO_DEVICE;
+    // activations as [n tokens] x [k] fp16; box = one unit: tile_tok tokens x chunk_k columns
+    CUtensorMap mx;
+    if (!make_tensor_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.x, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.k * 2,
+                            (uint32_t)chunk_k, (uint32_t)c.tile_tok, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return TUNA_ERR_NO_DEVICE;
     for (int tok0 = 0; tok0 < a.n; tok0 += c.tile_tok) {
         p.tok0 = tok0;
         int st;
-        switch (c.tile_tok) {
-            case 16: st = launch_ts<16>(p, ctas, a.stream); break;
-            case 32: st = launch_ts<32>(p, ctas, a.stream); break;
-            case 64: st = launch_ts<64>(p, ctas, a.stream); break;
+        switch (c.tile_tok * 10 + steps) {
+            case 164: st = launch_ts<16, 4>(p, mq, mx, ctas, a.stream); break;
+            case 168: st = launch_ts<16, 8>(p, mq, mx, ctas, a.stream); break;
+            case 324: st = launch_ts<32, 4>(p, mq, mx, ctas, a.stream); break;
+            case 328: st = launch_ts<32, 8>(p, mq, mx, ctas, a.stream); break;
+            case 644: st = launch_ts<64, 4>(p, mq, mx, ctas, a.stream); break;
+            case 648: st = launch_ts<64, 8>(p, mq, mx, ctas, a.stream); break;
             default: return TUNA_ERR_BAD_CONFIG;
         }
         if (st != TUNA_OK) return st;

@@ -57,7 +57,9 @@ static int resolve_config(int m, int n, int k, int sm_count, const tuna_config *
         for (int i = 0; i < kTableSize; ++i)
             if (kTable[i].m == m && kTable[i].k == k && kTable[i].n_bucket == b) { c = kTable[i].cfg; break; }
     }
-    if (c.path == TUNA_PATH_AUTO) c.path = (n <= 32) ? TUNA_PATH_STREAM : TUNA_PATH_UMMA;
+    // No table entry: the tcgen05 weight-streaming kernel up to one 64-token pass (the regime
+    // bound by HBM), the TMA-staged tcgen05 kernel above it.
+    if (c.path == TUNA_PATH_AUTO) c.path = (n <= 64) ? TUNA_PATH_TSTREAM : TUNA_PATH_UMMA;
     int st;
     if (c.path == TUNA_PATH_STREAM) st = gemm_stream_normalize_config(m, n, k, sm_count, &c);
     else if (c.path == TUNA_PATH_UMMA) st = gemm_umma_normalize_config(m, n, k, sm_count, &c);

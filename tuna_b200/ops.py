@@ -149,20 +149,6 @@ def quantize(w, codebook=None):
     return q, (absmax, code)
 
 
-def matmul_host(x_host, q, s, c, o_host, m: int, n: int, k: int, *, x_dev=None, o_dev=None) -> None:
-    """The op with HOST activations and output: copies x (pinned host) to the device, runs the
-    GEMM against the resident weights and copies the result back, all on the current stream.
-    Weights, scales and codebook are parameters and stay on the device, as in the reference."""
-    dev = q.device
-    if x_dev is None:
-        x_dev = torch.empty((n, k), dtype=torch.float16, device=dev)
-    if o_dev is None:
-        o_dev = torch.empty((n, m), dtype=torch.float16, device=dev)
-    x_dev.copy_(x_host, non_blocking=True)
-    matmul(x_dev, q, s, c, o_dev, m, n, k)
-    o_host.copy_(o_dev, non_blocking=True)
-
-
 class HostPipeline:
     """`matmul` for callers whose activations and outputs live in (pinned) HOST memory, with the
     copies overlapped with the GEMMs of neighbouring calls.

@@ -36,6 +36,10 @@ STREAM_SPACE = {
     "warps_k": (1, 2, 4, 8, 16),
     "k_steps": (4, 8, 16, 32, 64),
 }
+TSTREAM_SPACE = {
+    "row_blocks": (1, 2, 4),
+    "k_steps": (4, 8),
+}
 UMMA_SPACE = {
     "row_blocks": (1, 2, 3, 4),
     "stages_w": (2, 4, 6, 8),
@@ -45,8 +49,29 @@ UMMA_SPACE = {
 }
 
 
+PATH_IDS = {"stream": _lib.PATH_STREAM, "umma": _lib.PATH_UMMA, "tstream": _lib.PATH_TSTREAM}
+
+
 def space_for(path: str) -> dict:
-    return STREAM_SPACE if path == "stream" else UMMA_SPACE
+    return {"stream": STREAM_SPACE, "tstream": TSTREAM_SPACE, "umma": UMMA_SPACE}[path]
+
+
+def candidate_paths(n: int) -> tuple:
+    """Kernel families worth measuring for a token count: the path is part of what is tuned
+    (the reference's table has one kernel and tunes its tile per bucket, kernel.cu:3022-3155)."""
+    if n <= 32:
+        return ("tstream", "stream")
+    if n <= 128:
+        return ("tstream", "umma")
+    return ("umma",)
+
+
+def tile_tok_for(path: str, n: int) -> int:
+    if path == "stream":
+        return 8 if n <= 8 else 16 if n <= 16 else 32
+    if path == "tstream":
+        return 16 if n <= 16 else 32 if n <= 32 else 64
+    return min(make_configs.token_bucket(n), 256)
 
 
 def random_genome(rng: random.Random, path: str) -> dict:
@@ -66,7 +91,7 @@ def crossover(rng: random.Random, a: dict, b: dict) -> dict:
 
 
 def to_config(path: str, tile_tok: int, genome: dict) -> _lib.TunaConfig:
-    cfg = _lib.TunaConfig(path=_lib.PATH_STREAM if path == "stream" else _lib.PATH_UMMA, tile_tok=tile_tok)
+    cfg = _lib.TunaConfig(path=PATH_IDS[path], tile_tok=tile_tok)
     for k, v in genome.items():
         setattr(cfg, k, int(v))
     return cfg
@@ -136,16 +161,23 @@ class Bench:
 
 
 def tune_shape(m: int, n: int, k: int, path: str, generations: int, population: int, seed: int,
-               state_path: Path, log=print) -> tuple[dict, float]:
+               state_path: Path, log=print, bench=None) -> tuple[dict, float]:
     lib = _lib.load()
     rng = random.Random(seed * 1000003 + m * 31 + k * 17 + n)
-    tile_tok = make_configs.token_bucket(n) if path == "umma" else (8 if n <= 8 else 16 if n <= 16 else 32)
-    if path == "umma":
-        tile_tok = min(tile_tok, 256)
+    tile_tok = tile_tok_for(path, n)
     key = f"{m}_{make_configs.token_bucket(n)}_{k}"
     state = json.loads(state_path.read_text()) if state_path.exists() else {}
-    entry = state.setdefault(key, {"measured": {}, "generation": 0, "population": []})
-    bench = Bench(m, n, k, seed)
+    entry = state.setdefault(f"{key}/{path}", {"measured": {}, "generation": 0, "population": []})
+    bench = bench or Bench(m, n, k, seed)
+    space = space_for(path)
+    size = 1
+    for v in space.values():
+        size *= len(v)
+    if size <= population:  # a space this small is simply enumerated
+        import itertools
+
+        entry["population"] = [dict(zip(space, vals)) for vals in itertools.product(*space.values())]
+        generations = min(generations, entry["generation"] + 1)
 
     def fitness(g: dict) -> float:
         gk = json.dumps(g, sort_keys=True)
@@ -175,7 +207,8 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--shapes", nargs="+", required=True, help="MxK pairs, e.g. 28672x4096")
     ap.add_argument("--tokens", nargs="+", type=int, default=[16])
-    ap.add_argument("--path", choices=["auto", "stream", "umma"], default="auto")
+    ap.add_argument("--path", choices=["auto", "stream", "tstream", "umma"], default="auto",
+                    help="auto: measure every kernel family that suits the token count and keep the fastest")
     ap.add_argument("--generations", type=int, default=5)
     ap.add_argument("--population", type=int, default=12)
     ap.add_argument("--seed", type=int, default=0)
@@ -186,14 +219,21 @@ def main(argv=None):
     for shape in args.shapes:
         m, k = (int(v) for v in shape.lower().split("x"))
         for n in args.tokens:
-            path = args.path if args.path != "auto" else ("stream" if n <= 32 else "umma")
-            best, us = tune_shape(m, n, k, path, args.generations, args.population, args.seed, args.state)
-            if us == float("inf"):
+            paths = (args.path,) if args.path != "auto" else candidate_paths(n)
+            bench = Bench(m, n, k, args.seed)
+            results = []
+            for path in paths:
+                best, us = tune_shape(m, n, k, path, args.generations, args.population, args.seed, args.state, bench=bench)
+                if us != float("inf"):
+                    results.append((us, path, best))
+            if not results:
                 print(f"{m}x{k} n={n}: no valid configuration found")
                 continue
-            tile_tok = (8 if n <= 8 else 16 if n <= 16 else 32) if path == "stream" else min(make_configs.token_bucket(n), 256)
-            pm[f"{m}_{make_configs.token_bucket(n)}_{k}"] = {"path": path, "tile_tok": tile_tok, **best, "us": round(us, 2)}
-            print(f"{m}x{k} n={n}: {us:.2f} us {best}")
+            us, path, best = min(results, key=lambda r: r[0])
+            note = ", ".join(f"{p_} {u:.2f} us" for u, p_, _ in sorted(results, key=lambda r: r[0]))
+            pm[f"{m}_{make_configs.token_bucket(n)}_{k}"] = {"path": path, "tile_tok": tile_tok_for(path, n), **best, "us": round(us, 2),
+                                                             "note": note}
+            print(f"{m}x{k} n={n}: {path} {us:.2f} us {best}   [{note}]", flush=True)
             args.param_map.write_text(json.dumps(pm, indent=1, sort_keys=True))
     make_configs.generate(args.param_map)
 

@@ -27,12 +27,18 @@ def test_validity_filter_matches_the_launcher(tuna_lib):
     assert tuner.is_valid(tuna_lib, 4096, 2048, 4096, umma)
     umma_bad = tuner.to_config("umma", 256, dict(row_blocks=2, stages_w=4, stages_x=4, stages_a=4, dequant_warps=16, k_accs=1))
     assert not tuner.is_valid(tuna_lib, 4096, 2048, 4096, umma_bad)
+    # combinations no GPU test exercises are refused by the launcher
+    for bad in (dict(dequant_warps=12), dict(k_accs=2), dict(stages_w=2), dict(row_blocks=3)):
+        g = dict(row_blocks=1, stages_w=4, stages_x=4, dequant_warps=16, k_accs=1)
+        g.update(bad)
+        assert not tuner.is_valid(tuna_lib, 4096, 2048, 4096, tuner.to_config("umma", 64, g))
 
 
 def test_config_fields_round_trip():
-    cfg = tuner.to_config("umma", 64, dict(row_blocks=2, stages_w=6, stages_x=4, stages_a=8, dequant_warps=8, k_accs=2))
+    cfg = tuner.to_config("umma", 64, dict(row_blocks=2, stages_w=6, stages_x=4, stages_a=8, dequant_warps=8, k_accs=1))
     d = cfg.as_dict()
-    assert d["path"] == _lib.PATH_UMMA and d["tile_tok"] == 64 and d["row_blocks"] == 2 and d["k_accs"] == 2
+    assert d["path"] == _lib.PATH_UMMA and d["tile_tok"] == 64 and d["row_blocks"] == 2 and d["k_accs"] == 1
+    assert all(v == (0,) for v in tuner.UMMA_SPACE.values())  # the TMA-staged kernel: defaults only
 
 
 def test_path_is_part_of_the_search():

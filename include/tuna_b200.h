@@ -164,6 +164,31 @@ int tuna_matmul_batched(const void *q, const void *x, const void *code, const vo
 size_t tuna_matmul_batched_workspace_bytes(int m, int n, int k, int batch);
 
 /*
+ * `count` independent GEMMs - every x, q, absmax ready when the call is enqueued, every o written by
+ * it, one shared codebook - in ONE persistent launch: the units of all the GEMMs form one sequence
+ * that is cut evenly across the SMs, so small GEMMs (a Mistral attention projection is 1.3 us of
+ * HBM time) neither pay a launch each nor leave SMs idle, and the exchange of split-K partial sums
+ * of one GEMM overlaps with the streaming of the next.  This is how a layer's or a model's
+ * weight-streaming GEMMs are meant to be issued when their inputs do not depend on each other
+ * (QKV and gate+up of a layer, the experts of a mixture, a benchmark sweep); the reference has no
+ * counterpart (its README sums single-GEMM times, README.md:25-27).  Shapes, layouts and results
+ * as tuna_matmul; token counts up to 64 run in the sequence kernel (64 GEMMs per launch), a
+ * sequence with a larger token count is issued GEMM by GEMM.  Workspace:
+ * tuna_matmul_sequence_workspace_bytes (zero before the first use, left clean).
+ */
+typedef struct tuna_gemm_desc {
+    const void *q;      /* u8   [m/8, k/8, 32] */
+    const void *x;      /* fp16 [n, k]         */
+    const void *absmax; /* fp32 [m]            */
+    void *o;            /* fp16 [n, m]         */
+    int32_t m, n, k;
+    int32_t reserved;
+} tuna_gemm_desc;
+int tuna_matmul_sequence(const tuna_gemm_desc *gemms, int count, const void *code, void *workspace, size_t workspace_bytes,
+                         void *stream);
+size_t tuna_matmul_sequence_workspace_bytes(const tuna_gemm_desc *gemms, int count);
+
+/*
  * Quantizer: w fp16 [m, k] row-major -> packed codes q [m/8, k/8, 32] + absmax fp32 [m], for the
  * codebook `code` fp32 [16].  Replaces the reference's quantize_blockwise_dynamic_4bit(w,
  * block_size = k, preprocess = True) (test.py:7-68, a chain of torch kernels) with two kernels;

@@ -33,6 +33,13 @@ class TunaConfig(ctypes.Structure):
         return {n: getattr(self, n) for n, _ in self._fields_ if n != "reserved"}
 
 
+class TunaGemmDesc(ctypes.Structure):
+    """Mirror of `struct tuna_gemm_desc` (one GEMM of tuna_matmul_sequence)."""
+
+    _fields_ = [("q", c_void_p), ("x", c_void_p), ("absmax", c_void_p), ("o", c_void_p),
+                ("m", c_int32), ("n", c_int32), ("k", c_int32), ("reserved", c_int32)]
+
+
 PATH_AUTO, PATH_STREAM, PATH_UMMA, PATH_TSTREAM = 0, 1, 2, 3
 
 # every symbol include/tuna_b200.h declares: name -> (restype, argtypes)
@@ -43,6 +50,8 @@ SYMBOLS = {
     "tuna_matmul_batched": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_size_t] * 4 + [c_void_p, c_size_t, c_void_p]),
     "tuna_matmul_batched_workspace_bytes": (c_size_t, [c_int] * 4),
     "tuna_matmul_noalloc": (c_int, [c_void_p] * 5 + [c_int] * 3 + [c_void_p]),
+    "tuna_matmul_sequence": (c_int, [ctypes.POINTER(TunaGemmDesc), c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "tuna_matmul_sequence_workspace_bytes": (c_size_t, [ctypes.POINTER(TunaGemmDesc), c_int]),
     "tuna_lookup_config": (c_int, [c_int] * 3 + [ctypes.POINTER(TunaConfig)]),
     "tuna_dequant": (c_int, [c_void_p] * 4 + [c_int] * 2 + [c_void_p]),
     "tuna_quantize": (c_int, [c_void_p] * 4 + [c_int] * 2 + [c_void_p]),

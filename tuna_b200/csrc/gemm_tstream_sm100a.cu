@@ -113,23 +113,42 @@ constexpr int kTsDequantWarp0 = 8;
 constexpr int kTsDequantWarps = 16;
 constexpr int kTsThreads = 32 * (kTsDequantWarp0 + kTsDequantWarps);
 
-struct TsParams {
-    const float *code;
+constexpr int kTsMaxSeq = 64;  // GEMMs of one launch (tuna_matmul_sequence)
+
+// One GEMM of a launch.  The two tensor maps are what the copy producer hands to TMA; everything
+// else is read by the epilogue warps and the cursors.
+struct __align__(64) TsGemm {
+    CUtensorMap map_q;   // packed weights as [m/8 row groups] x [k 32-bit words]
+    CUtensorMap map_x;   // activations as [n] x [k] fp16
     const float *absmax;
     __half *o;
+    int m, n, k;
+    int chunks;       // ceil(k / chunk columns)
+    int row_tiles;    // ceil(m / (128 RB))
+    int unit0;        // index of its first unit in the launch's unit sequence
+    int tile0;        // index of its first tile among the launch's tiles (arrival counters)
+    int pad_;
+};
+
+struct TsParams {
+    const float *code;
     float *partials;
     unsigned int *counters;
     DeviceStatus *status;
-    int m, n, k;
-    int tok0;         // first token of this pass
+    int count;        // GEMMs of this launch
+    int tok0;         // first token of this pass (0 unless a single GEMM runs as several passes)
     int row_blocks;   // RB: 128-row blocks per tile
     int a_slots;      // A-slot ring depth
     int a_base;       // first tensor-memory column of the A slots (behind the two accumulator buffers)
     int acc_cols;     // columns of one accumulator buffer
-    int chunks;       // ceil(k / chunk columns)
-    int row_tiles;    // ceil(m / (128 RB))
-    int units;        // row_tiles * chunks
+    int units;        // units of all the GEMMs
     int units_q, units_r;  // units = units_q * CTAs + units_r: the first units_r CTAs take units_q + 1
+};
+
+template <int MAXG>
+struct __align__(64) TsLaunch {
+    TsParams c;
+    TsGemm g[MAXG];
 };
 
 // Table lookup: the selected byte of w (two 4-bit codes) -> half2 of the two code values.  Entry e
@@ -150,10 +169,50 @@ __device__ __forceinline__ int ts_cta_of_unit(const TsParams &p, int u)
     return u < big ? u / (p.units_q + 1) : p.units_r + (u - big) / p.units_q;
 }
 
-// STEPS: 32-column steps per slot (4 or 8).
-template <int N_TILE, int STEPS>
-__global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const TsParams p, const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_x)
+// Position in a CTA's contiguous range of the launch's unit sequence (GEMM after GEMM, each
+// tile-major): which GEMM, which row tile, which K chunk.
+struct TsCursor {
+    int g, tile, chunk;
+    int chunks, row_tiles;  // of GEMM g
+    int left;               // units of the range still ahead, including the current one
+    bool seg_first;         // the current unit starts a segment (the units of one tile inside the range)
+    template <class Launch>
+    __device__ void init(const Launch &L, int u_begin, int n_units)
+    {
+        g = 0;
+        while (g + 1 < L.c.count && L.g[g + 1].unit0 <= u_begin) ++g;
+        chunks = L.g[g].chunks;
+        row_tiles = L.g[g].row_tiles;
+        const int r = u_begin - L.g[g].unit0;
+        tile = r / chunks;
+        chunk = r - tile * chunks;
+        left = n_units;
+        seg_first = true;
+    }
+    __device__ bool seg_last() const { return chunk + 1 == chunks || left == 1; }
+    template <class Launch>
+    __device__ void next(const Launch &L)
+    {
+        seg_first = seg_last();
+        --left;
+        if (++chunk == chunks) {
+            chunk = 0;
+            if (++tile == row_tiles && left > 0) {
+                tile = 0;
+                ++g;
+                chunks = L.g[g].chunks;
+                row_tiles = L.g[g].row_tiles;
+            }
+        }
+    }
+};
+
+// STEPS: 32-column steps per slot (4 or 8).  MAXG: capacity of the launch's GEMM table (1 for a
+// single GEMM, kTsMaxSeq for a sequence).
+template <int N_TILE, int STEPS, int MAXG>
+__global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const __grid_constant__ TsLaunch<MAXG> L)
 {
+    const TsParams &p = L.c;
     constexpr int kChunkK = 32 * STEPS;                     // columns of a unit / slot
     constexpr int kSlotCols = 16 * STEPS;                   // tensor-memory columns of one A slot
     constexpr int kSlotBytes = 16 * kChunkK * 4;            // packed bytes of a slot: 16 row groups x 4 bytes per column
@@ -205,7 +264,6 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     // this CTA's contiguous range of units
     const int u_begin = cta * p.units_q + min(cta, p.units_r);
     const int n_units = p.units_q + (cta < p.units_r ? 1 : 0);
-    const int tile0 = u_begin / p.chunks, chunk0 = u_begin - tile0 * p.chunks;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -256,11 +314,11 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         constexpr uint32_t idesc = make_idesc(N_TILE);
         constexpr uint32_t desc_hi = (kSbo >> 4) | (1u << 14);
         Ring ra, rx, rd;
-        int chunk = chunk0;
-        bool seg_first = true;  // first unit of a segment (the units of one tile inside the range)
+        TsCursor cur;
+        cur.init(L, u_begin, n_units);
         bool ok = true;
-        for (int u = 0; ok && u < n_units; ++u) {
-            const bool seg_last = (chunk + 1 == p.chunks) || (u + 1 == n_units);
+        for (int u = 0; ok && u < n_units; ++u, cur.next(L)) {
+            const bool seg_first = cur.seg_first, seg_last = cur.seg_last();
             TS_PROF_BEGIN
             if (seg_first) ok = mbar_wait(d_empty + 8 * rd.idx, rd.phase ^ 1, abort_flag, p.status, 3);
             TS_PROF_END(0)
@@ -301,8 +359,6 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
             }
             rx.advance(kXS);
             if (seg_last) rd.advance(2);
-            seg_first = seg_last;
-            if (++chunk == p.chunks) chunk = 0;
         }
     } else if (warp == 1 || warp == 3) {
         // ------------------------------------------------------------------ activation re-tiling
@@ -373,8 +429,10 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         // the first ring-full of their copies is issued before the dependency wait (and before
         // this warp joins the rest of the prologue); x may come from the kernel before this one.
         Ring rw, rn;
-        int sl = 0, w_tile = tile0, w_chunk = chunk0, w_rb = 0;
-        int xu = 0, x_chunk = chunk0;
+        int sl = 0, w_rb = 0, xu = 0;
+        TsCursor wc, xc;
+        wc.init(L, u_begin, n_units);
+        xc.init(L, u_begin, n_units);
         bool ok = true;
         auto issue_x = [&](bool blocking) {
             // as many activation copies as have a free stage (all the outstanding ones if `blocking`)
@@ -384,12 +442,12 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
                 if (!ok) break;
                 if (elect_one_sync()) {
                     mbar_expect_tx(xn_full + 8 * rn.idx, kXNatBytes);
-                    tma_load_2d(xnat + (uint32_t)rn.idx * kXNatBytes, &tmap_x, x_chunk * kChunkK, p.tok0, xn_full + 8 * rn.idx);
+                    tma_load_2d(xnat + (uint32_t)rn.idx * kXNatBytes, &L.g[xc.g].map_x, xc.chunk * kChunkK, p.tok0, xn_full + 8 * rn.idx);
                 }
                 __syncwarp();
                 rn.advance(kXN);
                 ++xu;
-                if (++x_chunk == p.chunks) x_chunk = 0;
+                xc.next(L);
             }
         };
         auto issue_w_until = [&](int end, bool with_x) {
@@ -401,13 +459,13 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
                 if (!ok) break;
                 if (elect_one_sync()) {
                     mbar_expect_tx(w_full + 8 * rw.idx, kSlotBytes);
-                    tma_load_2d(w_stage(rw.idx), &tmap_q, w_chunk * kChunkK, (w_tile * RB + w_rb) * 16, w_full + 8 * rw.idx);
+                    tma_load_2d(w_stage(rw.idx), &L.g[wc.g].map_q, wc.chunk * kChunkK, (wc.tile * RB + w_rb) * 16, w_full + 8 * rw.idx);
                 }
                 __syncwarp();
                 rw.advance(WS);
                 if (++w_rb == RB) {
                     w_rb = 0;
-                    if (++w_chunk == p.chunks) { w_chunk = 0; ++w_tile; }
+                    wc.next(L);
                 }
             }
         };
@@ -422,12 +480,15 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         const int tmem_lane = 32 * quarter + lane;
         const size_t slot_floats = (size_t)RB * kBlockRows * N_TILE;
         Ring rd;
-        int u = 0, tile = tile0, chunk = chunk0;
+        TsCursor cur;
+        cur.init(L, u_begin, n_units);
+        int u = 0;
         while (u < n_units) {
-            // the segment: chunks [c0, c1) of `tile`
-            const int c0 = chunk;
-            const int c1 = min(p.chunks, c0 + (n_units - u));
-            const bool full = (c0 == 0 && c1 == p.chunks);
+            // the segment: chunks [c0, c1) of tile `tile` of GEMM `cur.g`
+            const TsGemm &G = L.g[cur.g];
+            const int tile = cur.tile, c0 = cur.chunk;
+            const int c1 = min(G.chunks, c0 + cur.left);
+            const bool full = (c0 == 0 && c1 == G.chunks);
             TS_PROF_BEGIN
             if (!mbar_wait_warp(d_full + 8 * rd.idx, rd.phase, abort_flag, p.status, 6)) break;
             TS_PROF_END(0)
@@ -436,17 +497,17 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
             float *my_partial = p.partials + (size_t)(2 * cta + (c0 == 0 ? 1 : 0)) * slot_floats;
             for (int rb = 0; rb < RB; ++rb) {
                 const int row = (tile * RB + rb) * kBlockRows + row_in_block;
-                const float sc = (full && row < p.m) ? p.absmax[row] : 0.f;
+                const float sc = (full && row < G.m) ? G.absmax[row] : 0.f;
 #pragma unroll 1
                 for (int piece = 0; piece < N_TILE / 16; ++piece) {
                     float v[16];
                     tc_ld_x16(tmem + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(rd.idx * p.acc_cols) + (uint32_t)rb * N_TILE + piece * 16, v);
                     if (full) {
-                        if (row < p.m) {
+                        if (row < G.m) {
 #pragma unroll
                             for (int i = 0; i < 16; ++i) {
                                 const int tok = p.tok0 + piece * 16 + i;
-                                if (tok < p.n) p.o[(size_t)tok * p.m + row] = __float2half_rn(v[i] * sc);
+                                if (tok < G.n) G.o[(size_t)tok * G.m + row] = __float2half_rn(v[i] * sc);
                             }
                         }
                     } else {
@@ -466,10 +527,10 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
                 // range order and stores the rows.
                 __threadfence();
                 __syncwarp();
-                const int cta_first = ts_cta_of_unit(p, tile * p.chunks);
-                const int cta_last = ts_cta_of_unit(p, (tile + 1) * p.chunks - 1);
+                const int cta_first = ts_cta_of_unit(p, G.unit0 + tile * G.chunks);
+                const int cta_last = ts_cta_of_unit(p, G.unit0 + (tile + 1) * G.chunks - 1);
                 const int nseg = cta_last - cta_first + 1;
-                unsigned int *counter = p.counters + (size_t)tile * 4 + quarter;
+                unsigned int *counter = p.counters + (size_t)(G.tile0 + tile) * 4 + quarter;
                 unsigned int old = 0;
                 if (lane == 0) old = atomicAdd(counter, 1u);
                 old = __shfl_sync(0xffffffffu, old, 0);
@@ -478,8 +539,8 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
                     __threadfence();
                     for (int rb = 0; rb < RB; ++rb) {
                         const int row = (tile * RB + rb) * kBlockRows + row_in_block;
-                        if (row >= p.m) continue;
-                        const float sc = p.absmax[row];
+                        if (row >= G.m) continue;
+                        const float sc = G.absmax[row];
 #pragma unroll 1
                         for (int piece = 0; piece < N_TILE / 16; ++piece) {
                             float acc[16];
@@ -512,16 +573,15 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
 #pragma unroll
                             for (int i = 0; i < 16; ++i) {
                                 const int tok = p.tok0 + piece * 16 + i;
-                                if (tok < p.n) p.o[(size_t)tok * p.m + row] = __float2half_rn(acc[i] * sc);
+                                if (tok < G.n) G.o[(size_t)tok * G.m + row] = __float2half_rn(acc[i] * sc);
                             }
                         }
                     }
                 }
             }
             TS_PROF_END(1)
+            for (int i = c0; i < c1; ++i) cur.next(L);
             u += c1 - c0;
-            chunk = 0;
-            ++tile;
             rd.advance(2);
         }
     } else {
@@ -662,8 +722,8 @@ size_t gemm_tstream_workspace_bytes(int m, int n, int k, const tuna_config &c, i
     return partial_region_bytes(sm_count) + counters;
 }
 
-template <int N_TILE, int STEPS>
-static int launch_ts(const TsParams &p, const CUtensorMap &mq, const CUtensorMap &mx, int ctas, cudaStream_t stream)
+template <int N_TILE, int STEPS, int MAXG>
+static int launch_ts(const TsLaunch<MAXG> &L, int ctas, cudaStream_t stream)
 {
     static bool attr_set[64] = {false};  // one-time, per device, opt-in to large dynamic shared memory
     static std::mutex mu;
@@ -672,7 +732,7 @@ static int launch_ts(const TsParams &p, const CUtensorMap &mq, const CUtensorMap
     {
         std::lock_guard<std::mutex> lock(mu);
         if (!attr_set[dev]) {
-            if (cudaFuncSetAttribute(gemm_w4a16_tstream_kernel<N_TILE, STEPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            if (cudaFuncSetAttribute(gemm_w4a16_tstream_kernel<N_TILE, STEPS, MAXG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kTsSmemDynamic) != cudaSuccess)
                 return TUNA_ERR_NO_DEVICE;
             attr_set[dev] = true;
@@ -688,59 +748,144 @@ static int launch_ts(const TsParams &p, const CUtensorMap &mq, const CUtensorMap
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    return cudaLaunchKernelEx(&lc, gemm_w4a16_tstream_kernel<N_TILE, STEPS>, p, mq, mx) == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
+    return cudaLaunchKernelEx(&lc, gemm_w4a16_tstream_kernel<N_TILE, STEPS, MAXG>, L) == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
+}
+
+template <int MAXG>
+static int launch_ts_dispatch(const TsLaunch<MAXG> &L, int tile_tok, int steps, int ctas, cudaStream_t stream)
+{
+    switch (tile_tok * 10 + steps) {
+        case 164: return launch_ts<16, 4, MAXG>(L, ctas, stream);
+        case 168: return launch_ts<16, 8, MAXG>(L, ctas, stream);
+        case 324: return launch_ts<32, 4, MAXG>(L, ctas, stream);
+        case 328: return launch_ts<32, 8, MAXG>(L, ctas, stream);
+        case 644: return launch_ts<64, 4, MAXG>(L, ctas, stream);
+        case 648: return launch_ts<64, 8, MAXG>(L, ctas, stream);
+        default: return TUNA_ERR_BAD_CONFIG;
+    }
+}
+
+// Fills the table entry of one GEMM (tensor maps, geometry); `unit0` / `tile0` are where its units
+// and tiles start in the launch.  Returns its unit count, or a negative status.
+static long long ts_fill_gemm(TsGemm *g, const void *q, const void *x, const float *absmax, void *o, int m, int n, int k,
+                              int row_blocks, int steps, int tile_tok, int unit0, int tile0)
+{
+    const int chunk_k = 32 * steps;
+    std::memset(g, 0, sizeof(*g));
+    g->absmax = absmax; g->o = (__half *)o;
+    g->m = m; g->n = n; g->k = k;
+    g->chunks = div_up(k, chunk_k);
+    g->row_tiles = div_up(m, kBlockRows * row_blocks);
+    g->unit0 = unit0;
+    g->tile0 = tile0;
+    // packed weights as [m/8 row groups] x [k 32-bit words] (a row group is 4k bytes); box = one slot:
+    // 16 row groups x chunk_k words.  Rows and columns past the matrix are zero-filled by the copy.
+    if (!make_tensor_map_2d(&g->map_q, CU_TENSOR_MAP_DATA_TYPE_UINT32, q, (uint64_t)k, (uint64_t)m / 8, (uint64_t)k * 4,
+                            (uint32_t)chunk_k, 16, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return TUNA_ERR_NO_DEVICE;
+    // activations as [n tokens] x [k] fp16; box = one unit: tile_tok tokens x chunk_k columns
+    if (!make_tensor_map_2d(&g->map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, (uint64_t)k, (uint64_t)n, (uint64_t)k * 2,
+                            (uint32_t)chunk_k, (uint32_t)tile_tok, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return TUNA_ERR_NO_DEVICE;
+    return (long long)g->row_tiles * g->chunks;
+}
+
+static void ts_fill_common(TsParams *p, const tuna_config &c, int steps, void *workspace, int sm_count)
+{
+    p->row_blocks = c.row_blocks;
+    p->acc_cols = c.row_blocks * c.tile_tok < 32 ? 32 : c.row_blocks * c.tile_tok;  // 32-column allocation granule
+    p->a_base = 2 * p->acc_cols;
+    p->a_slots = (kTsTmemCols - p->a_base) / (16 * steps);
+    if (p->a_slots > kTsMaxASlots) p->a_slots = kTsMaxASlots;
+    p->partials = (float *)workspace;
+    p->counters = (unsigned int *)((uint8_t *)workspace + partial_region_bytes(sm_count));
 }
 
 int launch_gemm_tstream(const GemmArgs &a, const tuna_config &c)
 {
-    const int steps = ts_steps(c), chunk_k = 32 * steps, slot_cols = 16 * steps;
-    TsParams p;
-    std::memset(&p, 0, sizeof(p));
-    p.code = a.code; p.absmax = a.absmax; p.o = (__half *)a.o;
-    p.m = a.m; p.n = a.n; p.k = a.k;
-    p.row_blocks = c.row_blocks;
-    p.acc_cols = c.row_blocks * c.tile_tok < 32 ? 32 : c.row_blocks * c.tile_tok;  // 32-column allocation granule
-    p.a_base = 2 * p.acc_cols;
-    p.a_slots = (kTsTmemCols - p.a_base) / slot_cols;
-    if (p.a_slots > kTsMaxASlots) p.a_slots = kTsMaxASlots;
-    p.chunks = div_up(a.k, chunk_k);
-    p.row_tiles = div_up(a.m, kBlockRows * c.row_blocks);
-    const long long units = (long long)p.row_tiles * p.chunks;
-    if (units >= (1ll << 30)) return TUNA_ERR_TOO_LARGE;
-    p.units = (int)units;
-    p.status = device_status_word();
-    if (!p.status) return TUNA_ERR_NO_DEVICE;
+    const int steps = ts_steps(c);
+    TsLaunch<1> L;
+    std::memset(&L.c, 0, sizeof(L.c));
+    L.c.code = a.code;
+    L.c.count = 1;
+    L.c.status = device_status_word();
+    if (!L.c.status) return TUNA_ERR_NO_DEVICE;
     if (a.workspace == nullptr || a.workspace_bytes < gemm_tstream_workspace_bytes(a.m, a.n, a.k, c, a.sm_count))
         return TUNA_ERR_WORKSPACE;
-    p.partials = (float *)a.workspace;
-    p.counters = (unsigned int *)((uint8_t *)a.workspace + partial_region_bytes(a.sm_count));
+    ts_fill_common(&L.c, c, steps, a.workspace, a.sm_count);
+    const long long units = ts_fill_gemm(&L.g[0], a.q, a.x, a.absmax, a.o, a.m, a.n, a.k, c.row_blocks, steps, c.tile_tok, 0, 0);
+    if (units < 0) return (int)units;
+    if (units >= (1ll << 30)) return TUNA_ERR_TOO_LARGE;
+    L.c.units = (int)units;
     int ctas = c.ctas;
-    if (ctas > p.units) ctas = p.units;
-    p.units_q = p.units / ctas;
-    p.units_r = p.units % ctas;
-    // packed weights as [m/8 row groups] x [k 32-bit words] (a row group is 4k bytes); box = one slot:
-    // 16 row groups x chunk_k words.  Rows and columns past the matrix are zero-filled by the copy.
-    CUtensorMap mq;
-    if (!make_tensor_map_2d(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.q, (uint64_t)a.k, (uint64_t)a.m / 8, (uint64_t)a.k * 4,
-                            (uint32_t)chunk_k, 16, CU_TENSOR_MAP_SWIZZLE_NONE))
-        return TUNA_ERR_NO_DEVICE;
-    // activations as [n tokens] x [k] fp16; box = one unit: tile_tok tokens x chunk_k columns
-    CUtensorMap mx;
-    if (!make_tensor_map_2d(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.x, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.k * 2,
-                            (uint32_t)chunk_k, (uint32_t)c.tile_tok, CU_TENSOR_MAP_SWIZZLE_NONE))
-        return TUNA_ERR_NO_DEVICE;
+    if (ctas > L.c.units) ctas = L.c.units;
+    L.c.units_q = L.c.units / ctas;
+    L.c.units_r = L.c.units % ctas;
     for (int tok0 = 0; tok0 < a.n; tok0 += c.tile_tok) {
-        p.tok0 = tok0;
-        int st;
-        switch (c.tile_tok * 10 + steps) {
-            case 164: st = launch_ts<16, 4>(p, mq, mx, ctas, a.stream); break;
-            case 168: st = launch_ts<16, 8>(p, mq, mx, ctas, a.stream); break;
-            case 324: st = launch_ts<32, 4>(p, mq, mx, ctas, a.stream); break;
-            case 328: st = launch_ts<32, 8>(p, mq, mx, ctas, a.stream); break;
-            case 644: st = launch_ts<64, 4>(p, mq, mx, ctas, a.stream); break;
-            case 648: st = launch_ts<64, 8>(p, mq, mx, ctas, a.stream); break;
-            default: return TUNA_ERR_BAD_CONFIG;
+        L.c.tok0 = tok0;
+        const int st = launch_ts_dispatch(L, c.tile_tok, steps, ctas, a.stream);
+        if (st != TUNA_OK) return st;
+    }
+    return TUNA_OK;
+}
+
+// ---- a sequence of independent GEMMs in one persistent launch
+
+size_t gemm_tstream_sequence_workspace_bytes(const tuna_gemm_desc *d, int count, int sm_count)
+{
+    size_t tiles = 0;
+    for (int i = 0; i < count; ++i) tiles += (size_t)div_up(d[i].m, kBlockRows);
+    return partial_region_bytes(sm_count) + (tiles * 16 + 255) / 256 * 256;
+}
+
+// Whether the sequence kernel can take these GEMMs (token counts of one pass; the rest is checked by the caller).
+bool gemm_tstream_sequence_supported(const tuna_gemm_desc *d, int count)
+{
+    if (count < 1) return false;
+    for (int i = 0; i < count; ++i)
+        if (d[i].n > 64) return false;
+    return true;
+}
+
+int launch_gemm_tstream_sequence(const tuna_gemm_desc *d, int count, const float *code, void *workspace, size_t workspace_bytes,
+                                 int sm_count, cudaStream_t stream)
+{
+    if (workspace == nullptr || workspace_bytes < gemm_tstream_sequence_workspace_bytes(d, count, sm_count)) return TUNA_ERR_WORKSPACE;
+    DeviceStatus *status = device_status_word();
+    if (!status) return TUNA_ERR_NO_DEVICE;
+    int tile0 = 0;  // tiles of the GEMMs launched so far: every launch has its own counters
+    for (int first = 0; first < count; first += kTsMaxSeq) {
+        const int cnt = count - first < kTsMaxSeq ? count - first : kTsMaxSeq;
+        int max_n = 1;
+        for (int i = 0; i < cnt; ++i) max_n = d[first + i].n > max_n ? d[first + i].n : max_n;
+        tuna_config c;
+        std::memset(&c, 0, sizeof(c));
+        c.path = TUNA_PATH_TSTREAM;
+        c.tile_tok = max_n <= 16 ? 16 : (max_n <= 32 ? 32 : 64);
+        c.row_blocks = 1;   // 16-KB units: the whole sequence is balanced at that granularity
+        c.k_steps = 8;
+        c.ctas = sm_count;
+        static thread_local TsLaunch<kTsMaxSeq> L;  // ~20 KB: not on the stack
+        std::memset(&L.c, 0, sizeof(L.c));
+        L.c.code = code;
+        L.c.count = cnt;
+        L.c.status = status;
+        ts_fill_common(&L.c, c, 8, workspace, sm_count);
+        long long units = 0;
+        for (int i = 0; i < cnt; ++i) {
+            const tuna_gemm_desc &g = d[first + i];
+            const long long u = ts_fill_gemm(&L.g[i], g.q, g.x, (const float *)g.absmax, g.o, g.m, g.n, g.k, 1, 8, c.tile_tok, (int)units, tile0);
+            if (u < 0) return (int)u;
+            units += u;
+            tile0 += L.g[i].row_tiles;
+            if (units >= (1ll << 30)) return TUNA_ERR_TOO_LARGE;
         }
+        L.c.units = (int)units;
+        int ctas = c.ctas;
+        if (ctas > L.c.units) ctas = L.c.units;
+        L.c.units_q = L.c.units / ctas;
+        L.c.units_r = L.c.units % ctas;
+        const int st = launch_ts_dispatch(L, c.tile_tok, 8, ctas, stream);
         if (st != TUNA_OK) return st;
     }
     return TUNA_OK;

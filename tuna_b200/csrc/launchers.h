@@ -62,5 +62,10 @@ int gemm_umma_normalize_config(int m, int n, int k, int sm_count, tuna_config *c
 int launch_gemm_tstream(const GemmArgs &a, const tuna_config &cfg);
 size_t gemm_tstream_workspace_bytes(int m, int n, int k, const tuna_config &cfg, int sm_count);
 int gemm_tstream_normalize_config(int m, int n, int k, int sm_count, tuna_config *cfg);
+// The same kernel walking a table of independent GEMMs in one persistent launch (up to 64 per launch).
+bool gemm_tstream_sequence_supported(const tuna_gemm_desc *d, int count);
+size_t gemm_tstream_sequence_workspace_bytes(const tuna_gemm_desc *d, int count, int sm_count);
+int launch_gemm_tstream_sequence(const tuna_gemm_desc *d, int count, const float *code, void *workspace, size_t workspace_bytes,
+                                 int sm_count, cudaStream_t stream);
 
 }  // namespace tuna

@@ -170,6 +170,41 @@ extern "C" size_t tuna_matmul_batched_workspace_bytes(int m, int n, int k, int b
     return c.path == TUNA_PATH_STREAM ? gemm_stream_workspace_bytes(m, n, k, c, sms, batch) : workspace_for(m, n, k, c, sms);
 }
 
+extern "C" size_t tuna_matmul_sequence_workspace_bytes(const tuna_gemm_desc *g, int count)
+{
+    if (!g || count < 1) return 0;
+    const int sms = device_sm_count();
+    size_t need = gemm_tstream_sequence_supported(g, count) ? gemm_tstream_sequence_workspace_bytes(g, count, sms) : 0;
+    for (int i = 0; i < count; ++i) {  // the fallback issues them one by one on the same workspace
+        const size_t w = tuna_matmul_workspace_bytes(g[i].m, g[i].n, g[i].k);
+        if (w == 0) return 0;
+        need = w > need ? w : need;
+    }
+    return need;
+}
+
+extern "C" int tuna_matmul_sequence(const tuna_gemm_desc *g, int count, const void *code, void *workspace, size_t workspace_bytes,
+                                    void *stream)
+{
+    if (!g || !code) return TUNA_ERR_NULL_POINTER;
+    if (count < 1) return TUNA_ERR_BAD_SHAPE;
+    for (int i = 0; i < count; ++i) {
+        if (!g[i].q || !g[i].x || !g[i].absmax || !g[i].o) return TUNA_ERR_NULL_POINTER;
+        const int st = check_shape(g[i].m, g[i].n, g[i].k);
+        if (st != TUNA_OK) return st;
+        if (!aligned(g[i].q, 16) || !aligned(g[i].x, 16) || !aligned(g[i].o, 16) || !aligned(g[i].absmax, 4)) return TUNA_ERR_MISALIGNED;
+    }
+    if (!aligned(code, 4) || !aligned(workspace, 16)) return TUNA_ERR_MISALIGNED;
+    const int sms = device_sm_count();
+    if (gemm_tstream_sequence_supported(g, count))
+        return launch_gemm_tstream_sequence(g, count, (const float *)code, workspace, workspace_bytes, sms, (cudaStream_t)stream);
+    for (int i = 0; i < count; ++i) {
+        const int st = tuna_matmul(g[i].q, g[i].x, code, g[i].absmax, g[i].o, g[i].m, g[i].n, g[i].k, workspace, workspace_bytes, stream);
+        if (st != TUNA_OK) return st;
+    }
+    return TUNA_OK;
+}
+
 extern "C" int tuna_matmul(const void *q, const void *x, const void *code, const void *absmax, void *o,
                            int m, int n, int k, void *workspace, size_t workspace_bytes, void *stream)
 {

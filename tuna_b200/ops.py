@@ -115,6 +115,53 @@ def matmul_batched(x, q, s, c, o, m: int, n: int, k: int, *, workspace=None) -> 
                                       ws.data_ptr(), ws.numel(), _stream_ptr(dev)))
 
 
+class MatmulSequence:
+    """`count` independent GEMMs issued as ONE persistent launch (`tuna_matmul_sequence`).
+
+    Built once from the tensors of every GEMM - `gemms` is a list of `(x, q, s, o, m, n, k)` with the
+    layouts of `matmul`, `c` the shared codebook - and run any number of times with `run()`, on the
+    current stream of the tensors' device.  The tensors are referenced, not copied: their
+    contents may change between runs, their addresses may not.  The inputs of all the GEMMs must
+    be ready when `run()` is enqueued (the GEMMs do not depend on each other)."""
+
+    def __init__(self, gemms, c, *, workspace=None):
+        if not gemms:
+            raise ValueError("an empty sequence")
+        self.device = gemms[0][0].device
+        self.count = len(gemms)
+        self._keep = []
+        self._descs = (_lib.TunaGemmDesc * self.count)()
+        for i, (x, q, s, o, m, n, k) in enumerate(gemms):
+            _expect(x, "x", torch.float16, n * k, self.device)
+            _expect(q, "q", torch.uint8, m * k // 2, self.device)
+            _expect(s, "s", torch.float32, m, self.device)
+            _expect(o, "o", torch.float16, n * m, self.device)
+            self._descs[i] = _lib.TunaGemmDesc(q.data_ptr(), x.data_ptr(), s.data_ptr(), o.data_ptr(), m, n, k, 0)
+            self._keep.append((x, q, s, o))
+        _expect(c, "c", torch.float32, 16, self.device)
+        self.code = c
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            need = int(lib.tuna_matmul_sequence_workspace_bytes(self._descs, self.count))
+            if need == 0:
+                raise ValueError("a GEMM of the sequence has an unsupported shape (m and k multiples of 8, n >= 1)")
+            if workspace is None:
+                workspace = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=self.device)
+            elif workspace.numel() * workspace.element_size() < need:
+                raise ValueError("workspace too small for this sequence")
+        self.workspace = workspace
+
+    def run(self) -> None:
+        with torch.cuda.device(self.device):
+            check(_lib.load().tuna_matmul_sequence(self._descs, self.count, self.code.data_ptr(), self.workspace.data_ptr(),
+                                                   self.workspace.numel() * self.workspace.element_size(), _stream_ptr(self.device)))
+
+
+def matmul_sequence(gemms, c, *, workspace=None) -> None:
+    """One-shot form of `MatmulSequence`: `gemms` is a list of `(x, q, s, o, m, n, k)`."""
+    MatmulSequence(gemms, c, workspace=workspace).run()
+
+
 def dequant(q, absmax, codebook, o, m: int, k: int) -> None:
     """`tuna.dequant(q, absmax, codebook, o, m, k)` (extension.cpp:40-49); o fp16 [m,k]."""
     dev = q.device if isinstance(q, torch.Tensor) else None

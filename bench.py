@@ -598,7 +598,23 @@ def main():
     if world > 1:
         o_layer = [[torch.empty_like(o_dev[i]) if g["kind"] == "row" else None for i, g in enumerate(per)] for per in gemms]
 
+    # The step through the sequence API: every GEMM of the step (all layers) in persistent launches
+    # of up to 64 GEMMs (tuna_matmul_sequence); every GEMM has its own output.  The all-reduces of
+    # the K-split layers follow the launch (asynchronously, joined at the end of the step).
+    o_seq = [[torch.empty((tokens, g["m"]), dtype=torch.float16, device=dev) for g in per] for per in gemms]
+    seq_gemms = [(x_dev[i], g["q"], g["s"], o_seq[li][i], g["m"], tokens, g["k"]) for li, per in enumerate(gemms) for i, g in enumerate(per)]
+    seq = tuna_b200.MatmulSequence(seq_gemms, code)
+    ws = seq.workspace  # sized for the sequence and for every GEMM of it on its own
+
     def step_device(collectives=True):
+        seq.run()
+        if collectives and world > 1:
+            pending = [dist.all_reduce(o_seq[li][i], async_op=True) for li, per in enumerate(gemms) for i, g in enumerate(per) if g["kind"] == "row"]
+            for h in pending:
+                h.wait()
+
+    # The same step GEMM by GEMM (tuna_matmul, one launch each): reported beside the headline
+    def step_per_call(collectives=True):
         pending = []
         for li, per in enumerate(gemms):
             for i, g in enumerate(per):
@@ -610,19 +626,29 @@ def main():
             h.wait()
 
     # end to end: every GEMM takes its activations from pinned HOST memory and returns its output
-    # there, through the package's host-buffer API (copies on their own streams, overlapped with
-    # the neighbouring GEMMs); the step ends when the last output has reached the host
-    pipe = tuna_b200.HostPipeline(dev, max(t.numel() for t in x_host), max(t.numel() for t in o_host), depth=4)
+    # there, through the package's host-buffer API: the sequence in 4 groups, group j's copy-in,
+    # group j-1's launch and group j-2's copy-out overlapping on three streams; the step ends when
+    # the last output has reached the host
+    x_host_l = [[x_host[i] for i, _ in enumerate(per)] for per in gemms]
+    o_host_l = [[torch.empty((tokens, g["m"]), dtype=torch.float16).pin_memory() for g in per] for per in gemms]
+    host_gemms = [(x_host_l[li][i], g["q"], g["s"], o_host_l[li][i], g["m"], tokens, g["k"]) for li, per in enumerate(gemms) for i, g in enumerate(per)]
+    row_flags = [g["kind"] == "row" for per in gemms for g in per]
+
+    def reduce_rows(outs, _state={"pos": 0}):
+        # the groups arrive in order; all-reduce the K-split layers' outputs of this group
+        base = _state["pos"]
+        for j, od in enumerate(outs):
+            if row_flags[(base + j) % len(row_flags)]:
+                dist.all_reduce(od)
+        _state["pos"] = (base + len(outs)) % len(row_flags)
+
+    hseq = tuna_b200.HostSequence(host_gemms, code, groups=4, after_group=reduce_rows if world > 1 else None)
 
     def step_e2e():
-        pipe.begin()
-        for per in gemms:
-            for i, g in enumerate(per):
-                reduce = (lambda od: dist.all_reduce(od)) if (g["kind"] == "row" and world > 1) else None
-                pipe.matmul(x_host[i], g["q"], g["s"], code, o_host[i], g["m"], tokens, g["k"], workspace=ws, after_gemm=reduce)
-        pipe.join()
+        hseq.run()
 
-    launches_per_step = layers * len(shapes)
+    launches_per_step = -(-(layers * len(shapes)) // 64)  # persistent launches of up to 64 GEMMs
+    gemms_per_step = layers * len(shapes)
     total_bytes = layers * sum(alg_bytes(m, tokens, k) for _, m, k in shapes)
 
     def capture(fn):
@@ -644,6 +670,8 @@ def main():
     inner = args.inner if args.inner > 0 else inner_for(run_dev, args.steps)
     ms_step = timed(run_dev, args.steps, args.warmup, inner)
     ms_eager = timed(step_device, max(args.steps // 4, 3), 2) if graph is not None else ms_step
+    pc_graph = None if args.no_graph else capture(step_per_call)
+    ms_per_call = timed(pc_graph.replay if pc_graph is not None else step_per_call, args.steps, args.warmup, max(1, inner // 2))
     ms_gemm_only = None
     if world > 1:
         g2 = None if args.no_graph else capture(lambda: step_device(False))
@@ -656,7 +684,6 @@ def main():
                 step_e2e()
                 stream.synchronize()
                 torch.cuda.synchronize()
-                pipe.reset()
                 e2e_graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(e2e_graph, stream=stream):
                     step_e2e()
@@ -717,9 +744,22 @@ def main():
             "timing": "that GEMM alone over the layers' distinct weights, CUDA-graph replay, CUDA events",
         }
 
+    # the launch that dominates the timed region is the sequence kernel itself: one launch = one step
+    roofline_single = roofline
+    if tokens < 256:
+        seq_traffic = DRAM_TRAFFIC_PER_LAUNCH.get(("sequence", args.workload, world))
+        roofline = {
+            "bound": "hbm", "achieved": total_bytes / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+            "frac": total_bytes / (ms_step * 1e-3) / 1e9 / peak,
+            "traffic": seq_traffic[0] if seq_traffic else None, "traffic_source": seq_traffic[1] if seq_traffic else None,
+            "kernel": "gemm_w4a16_tstream_kernel (tcgen05 weight streaming), one persistent launch over the step's %d GEMMs" % gemms_per_step,
+            "us_per_launch": ms_step * 1e3 / launches_per_step, "algorithmic_bytes_per_launch": total_bytes / launches_per_step,
+            "peak_source": f"{peak_kind} copy bandwidth", "timing": "CUDA events around the timed region (graph replays of the step), divided by the launches in it",
+        }
+
     extras = None
     if world == 1 and not args.no_extras and args.workload == "mistral7b_mlp_m16" and args.layers == 0:
-        gemms, graph, dom_graph, e2e_graph = None, None, None, None  # free the headline's weights first
+        gemms, graph, dom_graph, e2e_graph, pc_graph, seq, hseq, seq_gemms, host_gemms = (None,) * 9  # free the headline's weights first
         torch.cuda.empty_cache()
         try:
             extras = run_extras(dev, stream, timed, code, args.steps)
@@ -757,14 +797,17 @@ def main():
             "timed_region": f"{args.steps} steps x {inner} back-to-back replays of the step = {args.steps * inner * ms_step / 1e3:.2f} s; ms_per_step is per replay",
         },
         "inner_repeats": inner,
-        "us_per_gemm_avg": ms_step * 1e3 / launches_per_step,
+        "us_per_gemm_avg": ms_step * 1e3 / gemms_per_step,
+        "api": "tuna_matmul_sequence: the step's GEMMs as persistent launches of up to 64 GEMMs; `per_call` is the same step through tuna_matmul, one launch per GEMM",
+        "per_call": {"ms_per_step": ms_per_call, "value": total_bytes / (ms_per_call * 1e-3) / 1e9, "unit": "GB/s", "launch": "CUDA graph replay of 64 tuna_matmul calls"},
         "pct_of_8tbs": gbs / 8000.0 * 100.0,
         "eager_ms_per_step": ms_eager,
         "roofline": roofline,
+        "roofline_single_gemm": roofline_single,
         "cpu_baseline": cpu,
         "e2e": {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "inner_repeats": inner_e2e,
-                "how": "every GEMM called through tuna_b200.HostPipeline with pinned HOST activations and outputs (copy-in, GEMM and copy-out on three streams, 4 staging slots); weights resident (they are parameters)", "launch": e2e_launch},
+                "how": "tuna_b200.HostSequence: pinned HOST activations and outputs of every GEMM, the step in 4 groups (copy-in of a group, launch of the previous one, copy-out of the one before on three streams); weights resident (they are parameters)", "launch": e2e_launch},
         "gpu_launches": launches_per_step * args.steps * inner,
         "clocks": clocks,
         "parity": parity,

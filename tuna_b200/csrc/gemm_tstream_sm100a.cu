@@ -655,6 +655,10 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
                 // rows 0, 1 -> lanes g, g+8; rows 2, 3 -> lanes g+16, g+24
 #ifdef TS_ABL_NOST  // timing experiment: keep the lookups alive, skip the stores
                 asm volatile("" ::"r"(c[0][0] ^ c[0][1] ^ c[0][2] ^ c[0][3] ^ c[1][0] ^ c[1][1] ^ c[1][2] ^ c[1][3] ^ c[2][0] ^ c[2][1] ^ c[2][2] ^ c[2][3] ^ c[3][0] ^ c[3][1] ^ c[3][2] ^ c[3][3]), "r"(ta));
+#elif defined(TS_ABL_ST32)  // timing experiment (wrong layout): one 32-lane store per step instead of two 16-lane ones
+                asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(ta + 16u * st),
+                             "r"(c[0][0]), "r"(c[0][1]), "r"(c[0][2]), "r"(c[0][3]), "r"(c[1][0]), "r"(c[1][1]), "r"(c[1][2]), "r"(c[1][3]),
+                             "r"(c[2][0]), "r"(c[2][1]), "r"(c[2][2]), "r"(c[2][3]), "r"(c[3][0]), "r"(c[3][1]), "r"(c[3][2]), "r"(c[3][3]) : "memory");
 #else
                 tc_st_16x256b_x2(ta + 16u * st, c[0][0], c[0][1], c[1][0], c[1][1], c[0][2], c[0][3], c[1][2], c[1][3]);
                 tc_st_16x256b_x2(ta + (16u << 16) + 16u * st, c[2][0], c[2][1], c[3][0], c[3][1], c[2][2], c[2][3], c[3][2], c[3][3]);

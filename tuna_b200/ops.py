@@ -157,6 +157,79 @@ class MatmulSequence:
                                                    self.workspace.numel() * self.workspace.element_size(), _stream_ptr(self.device)))
 
 
+class HostSequence:
+    """`MatmulSequence` for callers whose activations and outputs live in (pinned) HOST memory.
+
+    The sequence is cut into `groups` contiguous groups; group j's activations are copied to the
+    device on a copy-in stream while group j-1 runs (one persistent launch per group, on the
+    caller's current stream) and group j-2's outputs travel back on a copy-out stream.
+    `gemms` is a list of `(x_host, q, s, o_host, m, n, k)`: pinned host tensors for x and o, device
+    tensors for the weights and scales (they are parameters and stay resident, as in the
+    reference).  `run()` returns at once; the current stream has waited for every copy-out when
+    it returns, so a stream or event synchronisation after it makes the host outputs readable.
+    `after_group(device_outputs)` (optional) runs on the compute stream between a group's launch
+    and its copy-out (e.g. the all-reduces of K-split layers).  A `run()` can be captured into a
+    CUDA graph (the host buffers are then fixed addresses read and written at every replay)."""
+
+    def __init__(self, gemms, c, *, groups: int = 4, after_group=None):
+        if not gemms:
+            raise ValueError("an empty sequence")
+        self.device = gemms[0][1].device
+        self.after_group = after_group
+        self.copy_in = torch.cuda.Stream(device=self.device)
+        self.copy_out = torch.cuda.Stream(device=self.device)
+        groups = max(1, min(int(groups), len(gemms)))
+        bounds = [round(i * len(gemms) / groups) for i in range(groups + 1)]
+        self._groups = []
+        workspace = None
+        for j in range(groups):
+            part = gemms[bounds[j]:bounds[j + 1]]
+            dev_gemms, pairs = [], []
+            for (xh, q, s_, oh, m, n, k) in part:
+                if not (xh.is_pinned() and oh.is_pinned()):
+                    raise ValueError("HostSequence needs pinned host tensors (pageable copies would serialise)")
+                xd = torch.empty((n, k), dtype=torch.float16, device=self.device)
+                od = torch.empty((n, m), dtype=torch.float16, device=self.device)
+                dev_gemms.append((xd, q, s_, od, m, n, k))
+                pairs.append((xh, xd, oh, od))
+            seq = MatmulSequence(dev_gemms, c, workspace=workspace)
+            if workspace is None or seq.workspace.numel() > workspace.numel():
+                workspace = seq.workspace  # the groups run one after the other on one stream: one workspace
+            self._groups.append({"seq": seq, "pairs": pairs, "in": torch.cuda.Event(), "done": torch.cuda.Event(), "out": torch.cuda.Event()})
+        need = max(g["seq"].workspace.numel() for g in self._groups)
+        if workspace.numel() < need:
+            workspace = torch.zeros(need, dtype=torch.uint8, device=self.device)
+        for g in self._groups:
+            g["seq"].workspace = workspace
+        self._fork = torch.cuda.Event()
+        self.copy_in.wait_stream(torch.cuda.current_stream(self.device))
+        self.copy_out.wait_stream(torch.cuda.current_stream(self.device))
+
+    def run(self) -> None:
+        compute = torch.cuda.current_stream(self.device)
+        # everything enqueued so far (the previous run's launches included) precedes this run's copies
+        self._fork.record(compute)
+        self.copy_in.wait_event(self._fork)
+        self.copy_out.wait_event(self._fork)
+        for g in self._groups:
+            with torch.cuda.stream(self.copy_in):
+                for xh, xd, _oh, _od in g["pairs"]:
+                    xd.copy_(xh, non_blocking=True)
+                g["in"].record(self.copy_in)
+            compute.wait_event(g["in"])
+            g["seq"].run()
+            if self.after_group is not None:
+                self.after_group([od for _xh, _xd, _oh, od in g["pairs"]])
+            g["done"].record(compute)
+            self.copy_out.wait_event(g["done"])
+            with torch.cuda.stream(self.copy_out):
+                for _xh, _xd, oh, od in g["pairs"]:
+                    oh.copy_(od, non_blocking=True)
+                g["out"].record(self.copy_out)
+        for g in self._groups:
+            compute.wait_event(g["out"])
+
+
 def matmul_sequence(gemms, c, *, workspace=None) -> None:
     """One-shot form of `MatmulSequence`: `gemms` is a list of `(x, q, s, o, m, n, k)`."""
     MatmulSequence(gemms, c, workspace=workspace).run()

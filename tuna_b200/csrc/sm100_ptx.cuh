@@ -50,8 +50,12 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
 {
     const long long t0 = clock64();
     for (;;) {
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < 64; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
+#ifdef TUNA_WAIT_BACKOFF
+            __nanosleep(TUNA_WAIT_BACKOFF);  // leave the issue slots to the warps that have work
+#endif
+        }
         if (*abort_flag) return false;
         if (clock64() - t0 > kWaitCycles) {
             *abort_flag = 1;

@@ -414,24 +414,37 @@ def run_extras(dev, stream, timed, code, steps):
                     if only is None or only == i:
                         tuna_b200.matmul(xs[i], sets[i][0][li], sets[i][1], code, os_[i], m, tokens, k, workspace=lib_ws)
 
+        # the sweep through the sequence API: every GEMM its own output
+        o_all = [[torch.empty((tokens, m), dtype=torch.float16, device=dev) for _, m, _k in shapes] for _ in range(layers)]
+        seq = tuna_b200.MatmulSequence([(xs[i], sets[i][0][li], sets[i][1], o_all[li][i], m, tokens, k)
+                                        for li in range(layers) for i, (_, m, k) in enumerate(shapes)], code)
         with torch.cuda.stream(stream):
+            seq.run()
+            stream.synchronize()
+            gs = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gs, stream=stream):
+                seq.run()
             sweep()
             stream.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
                 sweep()
+        ms_seq = timed(gs.replay, max(3, steps // 4), 2, max(1, int(50 / max(1.0, layers * len(shapes) * 0.02))))
         ms = timed(g.replay, max(3, steps // 4), 2)
         total = layers * sum(alg_bytes(m, tokens, k) for _, m, k in shapes)
         per_shape = []
         for i, (_, m, k) in enumerate(shapes):
             us = timed(lambda i=i: sweep(i), 3, 1) * 1e3 / layers
             cfg = tuna_b200.lookup_config(m, tokens, k)
-            per_shape.append(roofline_record(m, tokens, k, us, cfg.path, "that GEMM alone over the layers' distinct weights, eager back-to-back launches"))
+            per_shape.append(roofline_record(m, tokens, k, us, cfg.path, "that GEMM alone (tuna_matmul) over the layers' distinct weights, eager back-to-back launches"))
         hbm, _ = measured_peak()
-        out[name] = {"layers": layers, "tokens": tokens, "ms_per_sweep": ms, "gbs": total / (ms * 1e-3) / 1e9,
-                     "frac_hbm": total / (ms * 1e-3) / 1e9 / hbm, "bytes_per_sweep": total, "launch": "CUDA graph replay of the whole sweep",
-                     "gemms": per_shape}
-        del sets, g
+        out[name] = {"layers": layers, "tokens": tokens, "gemms": layers * len(shapes), "bytes_per_sweep": total,
+                     "sequence": {"ms_per_sweep": ms_seq, "gbs": total / (ms_seq * 1e-3) / 1e9, "frac_hbm": total / (ms_seq * 1e-3) / 1e9 / hbm,
+                                  "api": "tuna_matmul_sequence (persistent launches of up to 64 GEMMs), CUDA graph replay"},
+                     "per_call": {"ms_per_sweep": ms, "gbs": total / (ms * 1e-3) / 1e9, "frac_hbm": total / (ms * 1e-3) / 1e9 / hbm,
+                                  "api": "tuna_matmul, one launch per GEMM, CUDA graph replay of the whole sweep"},
+                     "gemms_alone": per_shape}
+        del sets, g, gs, seq, o_all
         torch.cuda.empty_cache()
 
     # ---- token sweep on the Llama-70B gate+up shape (BASELINE config 4)
@@ -601,17 +614,28 @@ def main():
     # The step through the sequence API: every GEMM of the step (all layers) in persistent launches
     # of up to 64 GEMMs (tuna_matmul_sequence); every GEMM has its own output.  The all-reduces of
     # the K-split layers follow the launch (asynchronously, joined at the end of the step).
-    o_seq = [[torch.empty((tokens, g["m"]), dtype=torch.float16, device=dev) for g in per] for per in gemms]
+    # (the K-split layers' outputs lie back to back in one buffer, so ONE all-reduce sums them all)
+    n_row = sum(1 for per in gemms for g in per if g["kind"] == "row")
+    row_elems = max([tokens * g["m"] for g in gemms[0] if g["kind"] == "row"], default=0)
+    o_rows = torch.empty((max(n_row, 1), max(row_elems, 1)), dtype=torch.float16, device=dev)
+    o_seq, r = [], 0
+    for per in gemms:
+        outs = []
+        for g in per:
+            if g["kind"] == "row":
+                outs.append(o_rows[r, :tokens * g["m"]].view(tokens, g["m"]))
+                r += 1
+            else:
+                outs.append(torch.empty((tokens, g["m"]), dtype=torch.float16, device=dev))
+        o_seq.append(outs)
     seq_gemms = [(x_dev[i], g["q"], g["s"], o_seq[li][i], g["m"], tokens, g["k"]) for li, per in enumerate(gemms) for i, g in enumerate(per)]
     seq = tuna_b200.MatmulSequence(seq_gemms, code)
     ws = seq.workspace  # sized for the sequence and for every GEMM of it on its own
 
     def step_device(collectives=True):
         seq.run()
-        if collectives and world > 1:
-            pending = [dist.all_reduce(o_seq[li][i], async_op=True) for li, per in enumerate(gemms) for i, g in enumerate(per) if g["kind"] == "row"]
-            for h in pending:
-                h.wait()
+        if collectives and world > 1 and n_row:
+            dist.all_reduce(o_rows)
 
     # The same step GEMM by GEMM (tuna_matmul, one launch each): reported beside the headline
     def step_per_call(collectives=True):
@@ -632,17 +656,13 @@ def main():
     x_host_l = [[x_host[i] for i, _ in enumerate(per)] for per in gemms]
     o_host_l = [[torch.empty((tokens, g["m"]), dtype=torch.float16).pin_memory() for g in per] for per in gemms]
     host_gemms = [(x_host_l[li][i], g["q"], g["s"], o_host_l[li][i], g["m"], tokens, g["k"]) for li, per in enumerate(gemms) for i, g in enumerate(per)]
-    row_flags = [g["kind"] == "row" for per in gemms for g in per]
+    pool_ids = [1 if g["kind"] == "row" else 0 for per in gemms for g in per]  # pool 1: outputs that need the all-reduce
 
-    def reduce_rows(outs, _state={"pos": 0}):
-        # the groups arrive in order; all-reduce the K-split layers' outputs of this group
-        base = _state["pos"]
-        for j, od in enumerate(outs):
-            if row_flags[(base + j) % len(row_flags)]:
-                dist.all_reduce(od)
-        _state["pos"] = (base + len(outs)) % len(row_flags)
+    def reduce_rows(pools):
+        if 1 in pools:
+            dist.all_reduce(pools[1])
 
-    hseq = tuna_b200.HostSequence(host_gemms, code, groups=4, after_group=reduce_rows if world > 1 else None)
+    hseq = tuna_b200.HostSequence(host_gemms, code, groups=4, after_group=reduce_rows if world > 1 else None, pool_ids=pool_ids)
 
     def step_e2e():
         hseq.run()
@@ -746,14 +766,16 @@ def main():
 
     # the launch that dominates the timed region is the sequence kernel itself: one launch = one step
     roofline_single = roofline
+    rank_bytes = sum(alg_bytes(g["m"], tokens, g["k"]) for per in gemms for g in per)  # this GPU's share of the step
     if tokens < 256:
         seq_traffic = DRAM_TRAFFIC_PER_LAUNCH.get(("sequence", args.workload, world))
         roofline = {
-            "bound": "hbm", "achieved": total_bytes / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-            "frac": total_bytes / (ms_step * 1e-3) / 1e9 / peak,
+            "bound": "hbm", "achieved": rank_bytes / (ms_step * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+            "frac": rank_bytes / (ms_step * 1e-3) / 1e9 / peak,
             "traffic": seq_traffic[0] if seq_traffic else None, "traffic_source": seq_traffic[1] if seq_traffic else None,
             "kernel": "gemm_w4a16_tstream_kernel (tcgen05 weight streaming), one persistent launch over the step's %d GEMMs" % gemms_per_step,
-            "us_per_launch": ms_step * 1e3 / launches_per_step, "algorithmic_bytes_per_launch": total_bytes / launches_per_step,
+            "us_per_launch": ms_step * 1e3 / launches_per_step, "algorithmic_bytes_per_launch": rank_bytes / launches_per_step,
+            "per": "GPU (one rank's launch over its shards; with N GPUs the step also contains the all-reduce)",
             "peak_source": f"{peak_kind} copy bandwidth", "timing": "CUDA events around the timed region (graph replays of the step), divided by the launches in it",
         }
 
@@ -816,7 +838,7 @@ def main():
         line["multi_gpu"] = {"gemm_only_ms_per_step": ms_gemm_only, "gemm_plus_allreduce_ms_per_step": ms_step,
                              "gemm_only_gbs": total_bytes / (ms_gemm_only * 1e-3) / 1e9 if ms_gemm_only else None,
                              "allgather_us": allgather_us,
-                             "note": "all-reduces of the K-split layers are issued asynchronously and joined at the end of the step; the all-gather that would reassemble a column-parallel output is timed alone, it is not part of the MLP step"}
+                             "note": "the K-split layers' partial outputs lie in one buffer and are summed by ONE all-reduce after the step's launch (per group of the sequence in the end-to-end path); the all-gather that would reassemble a column-parallel output is timed alone, it is not part of the MLP step"}
     if extras is not None:
         line["extras"] = extras
     print(json.dumps(line), flush=True)

@@ -123,6 +123,12 @@ int tuna_dequant(const void *q, const void *absmax, const void *code, void *o,
  * TUNA_ERR_DEVICE_TIMEOUT if a bounded mbarrier wait gave up. */
 int tuna_check_device_status(void *stream);
 
+/* Self-test of the bounded in-kernel waits: enqueues a one-warp kernel that waits, with a limit of
+ * about a millisecond, on a barrier nothing arrives at.  The wait gives up, the kernel returns, and
+ * the next tuna_check_device_status() reports TUNA_ERR_DEVICE_TIMEOUT (and clears the word).  The
+ * GPU is neither hung nor faulted by it. */
+int tuna_selftest_bounded_wait(void *stream);
+
 /*
  * The GEMM for callers that cannot allocate device memory.  It has no counterpart in the
  * reference.  Some hosts of this library run inside a region where cudaMalloc is off limits: an
@@ -173,7 +179,11 @@ size_t tuna_matmul_batched_workspace_bytes(int m, int n, int k, int batch);
  * (QKV and gate+up of a layer, the experts of a mixture, a benchmark sweep); the reference has no
  * counterpart (its README sums single-GEMM times, README.md:25-27).  Shapes, layouts and results
  * as tuna_matmul; token counts up to 64 run in the sequence kernel (64 GEMMs per launch), a
- * sequence with a larger token count is issued GEMM by GEMM.  Workspace:
+ * sequence with a larger token count is issued GEMM by GEMM.  Every GEMM has its own token
+ * count n, so this is also the grouped GEMM of a mixture of experts with a per-expert token
+ * list (the step the reference fakes with one combined GEMM over all experts,
+ * make_configs.py:105-106): one entry per expert, x and o pointing at that expert's rows, n its
+ * number of routed tokens; n = 0 (an expert without tokens) is skipped.  Workspace:
  * tuna_matmul_sequence_workspace_bytes (zero before the first use, left clean).
  */
 typedef struct tuna_gemm_desc {

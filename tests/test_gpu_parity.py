@@ -352,3 +352,19 @@ def test_wrapper_on_two_streams_uses_separate_scratch():
     torch.cuda.synchronize()
     for i in range(2):
         check_parity(outs[i].cpu().numpy(), orc.matmul_ref(*cases[i][0], m, n, k), TOL)
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_not_spun_on():
+    """The time-out path of the in-kernel waits, exercised without a real failure: a one-warp kernel
+    waits ~1 ms on a barrier nothing arrives at; the status word then reports the time-out once,
+    and the next GEMM on the same context runs normally."""
+    lib = _lib.load()
+    assert lib.tuna_check_device_status(stream_ptr()) == 0
+    assert lib.tuna_selftest_bounded_wait(stream_ptr()) == 0
+    assert lib.tuna_check_device_status(stream_ptr()) == -8  # TUNA_ERR_DEVICE_TIMEOUT, and the word is cleared
+    assert lib.tuna_check_device_status(stream_ptr()) == 0
+    m, n, k = 512, 16, 1024
+    host, dev = make_case(m, n, k, seed=77)
+    st, out, _ = run_matmul(dev, m, n, k)
+    assert st == 0
+    check_parity(out.cpu().numpy(), orc.matmul_ref(*host, m, n, k), TOL)

@@ -104,6 +104,33 @@ def test_sequence_mistral_mlp_layers_full_size():
         assert h.guards_intact()
 
 
+def test_sequence_as_grouped_gemm_with_per_expert_token_lists():
+    """Eight experts of one shape, unequal token counts (one expert without tokens): every expert's
+    rows of one shared activation / output buffer, one launch; parity per expert."""
+    m, k, experts = 1024, 2048, 8
+    counts = [5, 0, 16, 1, 9, 3, 12, 7]
+    rng = np.random.default_rng(3)
+    total = sum(counts)
+    x_all = torch.from_numpy(rng.standard_normal((total, k)).astype(np.float16)).cuda()
+    o_all = Guarded(total * m * 2, torch.float16, (total, m))
+    o_all.view.fill_(float("nan"))
+    gemms, hosts, off = [], [], 0
+    for e, n in enumerate(counts):
+        (x, q, absmax, code), (xd, qd, sd, cd) = make_case(m, max(n, 1), k, 200 + e)
+        gemms.append((x_all[off:off + n], qd, sd, o_all.view[off:off + n], m, n, k))
+        hosts.append((q, absmax, code, off, n))
+        off += n
+    tuna_b200.matmul_sequence(gemms, cd)
+    torch.cuda.synchronize()
+    assert _lib.load().tuna_check_device_status(stream_ptr()) == 0
+    xh = x_all.cpu().numpy()
+    got = o_all.view.cpu().numpy()
+    for q, absmax, code, off, n in hosts:
+        if n:
+            check_parity(got[off:off + n], orc.matmul_ref(xh[off:off + n], q, absmax, code, m, n, k), TOL)
+    assert o_all.guards_intact()
+
+
 def test_sequence_validates_its_arguments():
     lib = _lib.load()
     t = torch.zeros(256, dtype=torch.uint8, device="cuda")

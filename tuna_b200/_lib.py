@@ -56,6 +56,7 @@ SYMBOLS = {
     "tuna_dequant": (c_int, [c_void_p] * 4 + [c_int] * 2 + [c_void_p]),
     "tuna_quantize": (c_int, [c_void_p] * 4 + [c_int] * 2 + [c_void_p]),
     "tuna_check_device_status": (c_int, [c_void_p]),
+    "tuna_selftest_bounded_wait": (c_int, [c_void_p]),
     "tuna_status_string": (c_char_p, [c_int]),
     "tuna_abi_version": (c_int, []),
     "tuna_config_table_size": (c_int, []),

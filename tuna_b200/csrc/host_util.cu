@@ -4,6 +4,7 @@
 #include <mutex>
 #include "common.cuh"
 #include "launchers.h"
+#include "sm100_ptx.cuh"
 
 namespace tuna {
 
@@ -69,3 +70,33 @@ bool make_tensor_map_2d(CUtensorMap *map, CUtensorMapDataType dt, const void *ba
 }
 
 }  // namespace tuna
+
+// ------------------------------------------------------------------ self-test of the bounded waits
+//
+// Every mbarrier wait of the pipeline kernels gives up after a time limit, records where in the
+// device status word and lets the kernel unwind (tuna_check_device_status then reports
+// TUNA_ERR_DEVICE_TIMEOUT).  This entry point exercises exactly that path without a real failure:
+// one warp waits, with a limit of about a millisecond, on a barrier that nothing ever arrives at.
+namespace tuna {
+__global__ void bounded_wait_selftest_kernel(DeviceStatus *status, long long limit_cycles)
+{
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    // phase 0 of a barrier that expects one arrival and never gets it
+    if (!mbar_try_wait(smem_u32(&bar), 0)) mbar_wait_slow(smem_u32(&bar), 0, &s_abort, status, 99, limit_cycles);
+}
+}  // namespace tuna
+
+extern "C" int tuna_selftest_bounded_wait(void *stream)
+{
+    tuna::DeviceStatus *d = tuna::device_status_word();
+    if (!d) return TUNA_ERR_NO_DEVICE;
+    tuna::bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(d, 2000000ll);  // ~1 ms
+    return cudaGetLastError() == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
+}

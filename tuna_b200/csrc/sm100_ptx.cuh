@@ -46,7 +46,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
 // Bounded wait.  Returns false when the time limit ran out or another role raised the abort
 // flag; the caller unwinds.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                            DeviceStatus *status, int where)
+                                            DeviceStatus *status, int where, long long limit = kWaitCycles)
 {
     const long long t0 = clock64();
     for (;;) {
@@ -57,7 +57,7 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
 #endif
         }
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitCycles) {
+        if (clock64() - t0 > limit) {
             *abort_flag = 1;
             if (atomicCAS(&status->code, 0, where) == 0) status->detail = (int)blockIdx.x;
             return false;

@@ -6,6 +6,7 @@
 // time and every failure is a status code.
 #include <cstring>
 #include <mutex>
+#include <vector>
 #include "common.cuh"
 #include "launchers.h"
 
@@ -170,12 +171,28 @@ extern "C" size_t tuna_matmul_batched_workspace_bytes(int m, int n, int k, int b
     return c.path == TUNA_PATH_STREAM ? gemm_stream_workspace_bytes(m, n, k, c, sms, batch) : workspace_for(m, n, k, c, sms);
 }
 
+// The GEMMs of a sequence that have tokens (n = 0 is an expert nobody was routed to: nothing to do).
+static int sequence_compact(const tuna_gemm_desc *g, int count, std::vector<tuna_gemm_desc> *out)
+{
+    out->clear();
+    for (int i = 0; i < count; ++i) {
+        if (g[i].n == 0 && g[i].m > 0 && g[i].k > 0 && !(g[i].m % 8) && !(g[i].k % 8)) continue;
+        if (!g[i].q || !g[i].x || !g[i].absmax || !g[i].o) return TUNA_ERR_NULL_POINTER;
+        const int st = check_shape(g[i].m, g[i].n, g[i].k);
+        if (st != TUNA_OK) return st;
+        if (!aligned(g[i].q, 16) || !aligned(g[i].x, 16) || !aligned(g[i].o, 16) || !aligned(g[i].absmax, 4)) return TUNA_ERR_MISALIGNED;
+        out->push_back(g[i]);
+    }
+    return TUNA_OK;
+}
+
 extern "C" size_t tuna_matmul_sequence_workspace_bytes(const tuna_gemm_desc *g, int count)
 {
     if (!g || count < 1) return 0;
     const int sms = device_sm_count();
-    size_t need = gemm_tstream_sequence_supported(g, count) ? gemm_tstream_sequence_workspace_bytes(g, count, sms) : 0;
+    size_t need = gemm_tstream_sequence_workspace_bytes(g, count, sms);  // an upper bound whatever the token counts
     for (int i = 0; i < count; ++i) {  // the fallback issues them one by one on the same workspace
+        if (g[i].n == 0) continue;
         const size_t w = tuna_matmul_workspace_bytes(g[i].m, g[i].n, g[i].k);
         if (w == 0) return 0;
         need = w > need ? w : need;
@@ -188,18 +205,17 @@ extern "C" int tuna_matmul_sequence(const tuna_gemm_desc *g, int count, const vo
 {
     if (!g || !code) return TUNA_ERR_NULL_POINTER;
     if (count < 1) return TUNA_ERR_BAD_SHAPE;
-    for (int i = 0; i < count; ++i) {
-        if (!g[i].q || !g[i].x || !g[i].absmax || !g[i].o) return TUNA_ERR_NULL_POINTER;
-        const int st = check_shape(g[i].m, g[i].n, g[i].k);
-        if (st != TUNA_OK) return st;
-        if (!aligned(g[i].q, 16) || !aligned(g[i].x, 16) || !aligned(g[i].o, 16) || !aligned(g[i].absmax, 4)) return TUNA_ERR_MISALIGNED;
-    }
     if (!aligned(code, 4) || !aligned(workspace, 16)) return TUNA_ERR_MISALIGNED;
+    std::vector<tuna_gemm_desc> live;
+    int st = sequence_compact(g, count, &live);
+    if (st != TUNA_OK) return st;
+    if (live.empty()) return TUNA_OK;
     const int sms = device_sm_count();
-    if (gemm_tstream_sequence_supported(g, count))
-        return launch_gemm_tstream_sequence(g, count, (const float *)code, workspace, workspace_bytes, sms, (cudaStream_t)stream);
-    for (int i = 0; i < count; ++i) {
-        const int st = tuna_matmul(g[i].q, g[i].x, code, g[i].absmax, g[i].o, g[i].m, g[i].n, g[i].k, workspace, workspace_bytes, stream);
+    if (gemm_tstream_sequence_supported(live.data(), (int)live.size()))
+        return launch_gemm_tstream_sequence(live.data(), (int)live.size(), (const float *)code, workspace, workspace_bytes, sms,
+                                            (cudaStream_t)stream);
+    for (const tuna_gemm_desc &d : live) {
+        st = tuna_matmul(d.q, d.x, code, d.absmax, d.o, d.m, d.n, d.k, workspace, workspace_bytes, stream);
         if (st != TUNA_OK) return st;
     }
     return TUNA_OK;

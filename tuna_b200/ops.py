@@ -132,6 +132,10 @@ class MatmulSequence:
         self._keep = []
         self._descs = (_lib.TunaGemmDesc * self.count)()
         for i, (x, q, s, o, m, n, k) in enumerate(gemms):
+            if n == 0:  # an expert without tokens: the entry is skipped by the library
+                self._descs[i] = _lib.TunaGemmDesc(q.data_ptr(), 0, s.data_ptr(), 0, m, 0, k, 0)
+                self._keep.append((q, s))
+                continue
             _expect(x, "x", torch.float16, n * k, self.device)
             _expect(q, "q", torch.uint8, m * k // 2, self.device)
             _expect(s, "s", torch.float32, m, self.device)
@@ -167,11 +171,13 @@ class HostSequence:
     tensors for the weights and scales (they are parameters and stay resident, as in the
     reference).  `run()` returns at once; the current stream has waited for every copy-out when
     it returns, so a stream or event synchronisation after it makes the host outputs readable.
-    `after_group(device_outputs)` (optional) runs on the compute stream between a group's launch
-    and its copy-out (e.g. the all-reduces of K-split layers).  A `run()` can be captured into a
-    CUDA graph (the host buffers are then fixed addresses read and written at every replay)."""
+    `after_group(pools)` (optional) runs on the compute stream between a group's launch and its
+    copy-out; `pools` maps a pool id to ONE contiguous device tensor holding the outputs of the
+    group's GEMMs with that id (`pool_ids`, one int per GEMM, default 0) - e.g. the K-split layers'
+    partial outputs, which one all-reduce then sums.  A `run()` can be captured into a CUDA graph
+    (the host buffers are then fixed addresses read and written at every replay)."""
 
-    def __init__(self, gemms, c, *, groups: int = 4, after_group=None):
+    def __init__(self, gemms, c, *, groups: int = 4, after_group=None, pool_ids=None):
         if not gemms:
             raise ValueError("an empty sequence")
         self.device = gemms[0][1].device
@@ -182,20 +188,29 @@ class HostSequence:
         bounds = [round(i * len(gemms) / groups) for i in range(groups + 1)]
         self._groups = []
         workspace = None
+        pool_ids = list(pool_ids) if pool_ids is not None else [0] * len(gemms)
         for j in range(groups):
             part = gemms[bounds[j]:bounds[j + 1]]
+            ids = pool_ids[bounds[j]:bounds[j + 1]]
+            # one slab per pool: the outputs of a pool's GEMMs lie back to back (16-byte aligned pieces)
+            sizes = {}
+            for (xh, q, s_, oh, m, n, k), pid in zip(part, ids):
+                sizes[pid] = sizes.get(pid, 0) + (n * m + 7) // 8 * 8
+            slabs = {pid: torch.empty(sz, dtype=torch.float16, device=self.device) for pid, sz in sizes.items()}
+            used = {pid: 0 for pid in sizes}
             dev_gemms, pairs = [], []
-            for (xh, q, s_, oh, m, n, k) in part:
+            for (xh, q, s_, oh, m, n, k), pid in zip(part, ids):
                 if not (xh.is_pinned() and oh.is_pinned()):
                     raise ValueError("HostSequence needs pinned host tensors (pageable copies would serialise)")
                 xd = torch.empty((n, k), dtype=torch.float16, device=self.device)
-                od = torch.empty((n, m), dtype=torch.float16, device=self.device)
+                od = slabs[pid][used[pid]:used[pid] + n * m].view(n, m)
+                used[pid] += (n * m + 7) // 8 * 8
                 dev_gemms.append((xd, q, s_, od, m, n, k))
                 pairs.append((xh, xd, oh, od))
             seq = MatmulSequence(dev_gemms, c, workspace=workspace)
             if workspace is None or seq.workspace.numel() > workspace.numel():
                 workspace = seq.workspace  # the groups run one after the other on one stream: one workspace
-            self._groups.append({"seq": seq, "pairs": pairs, "in": torch.cuda.Event(), "done": torch.cuda.Event(), "out": torch.cuda.Event()})
+            self._groups.append({"seq": seq, "pairs": pairs, "pools": slabs, "in": torch.cuda.Event(), "done": torch.cuda.Event(), "out": torch.cuda.Event()})
         need = max(g["seq"].workspace.numel() for g in self._groups)
         if workspace.numel() < need:
             workspace = torch.zeros(need, dtype=torch.uint8, device=self.device)
@@ -219,7 +234,7 @@ class HostSequence:
             compute.wait_event(g["in"])
             g["seq"].run()
             if self.after_group is not None:
-                self.after_group([od for _xh, _xd, _oh, od in g["pairs"]])
+                self.after_group(g["pools"])
             g["done"].record(compute)
             self.copy_out.wait_event(g["done"])
             with torch.cuda.stream(self.copy_out):

@@ -145,7 +145,7 @@ int tuna_selftest_bounded_wait(void *stream);
  *    1024 rows, chosen with the configuration) plus two partial tiles per CTA, at most 18.5 MiB
  *    on a 148-SM part; with the largest partial tiles about 24 000 row tiles still fit.
  *  - The first call on a device looks up the arrays' device addresses (cudaGetSymbolAddress) and
- *    opts the kernel into large shared memory; make that first call outside any stream capture.
+ *    opts the kernel into large shared memory.
  *  - All calls share the one array per device and it keeps the previous call's contents (the part
  *    that must start at zero is cleared on the stream by every call): calls that overlap on the
  *    same GPU, on different streams, race.  Use tuna_matmul with separate workspaces for that.

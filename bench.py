@@ -77,20 +77,24 @@ def measured_peak(key: str = "hbm_gbs", fallback: float = FALLBACK_HBM_GBS):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+    """Samples SM clocks, power and throttle reasons with nvidia-smi; `stop()` summarises the samples
+    whose time stamps lie inside the timed regions that were registered with `window()`."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+    SETTLE_S = 0.15  # a sample this soon after the start of a region may still show the idle state
 
     def __init__(self, index: int):
         self.index = index
         self.samples = []
+        self.windows = []
         self.proc = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, bufsize=1)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -99,6 +103,15 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.samples.append(line.strip())
+
+    def window(self, t0: float, t1: float):
+        """Registers a timed region by its wall-clock start and end (time.time())."""
+        self.windows.append((t0, t1))
+
+    @staticmethod
+    def _stamp(text):
+        import datetime
+        return datetime.datetime.strptime(text, "%Y/%m/%d %H:%M:%S.%f").timestamp()
 
     def stop(self):
         if self.proc is None:
@@ -109,24 +122,33 @@ class ClockSampler:
             self.proc.wait(timeout=2)
         except Exception:
             pass
-        sm, mx, reasons = [], [], set()
+        sm, mx, watts, reasons, seen = [], [], [], set(), 0
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for s in list(self.samples):
             f = [t.strip() for t in s.split(",")]
-            if len(f) < 6:
+            if len(f) < 8:
                 continue
             try:
-                sm.append(float(f[0]))
-                mx.append(float(f[1]))
+                t = self._stamp(f[0])
+                clock, cmax = float(f[1]), float(f[2])
             except ValueError:
                 continue
-            for name, v in zip(names, f[2:6]):
+            seen += 1
+            mx.append(cmax)
+            if not any(t0 + self.SETTLE_S <= t <= t1 for t0, t1 in self.windows):
+                continue
+            sm.append(clock)
+            try:
+                watts.append(float(f[3]))
+            except ValueError:
+                pass
+            for name, v in zip(names, f[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
-        # the samples under load are the upper half (the sampler also sees set-up and idle gaps)
-        under_load = sorted(sm)[len(sm) // 2:] if sm else []
-        return {"sm_mhz": statistics.median(under_load) if under_load else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_min_mhz": min(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "power_w": statistics.median(watts) if watts else None,
+                "reasons": sorted(reasons), "samples": len(sm), "samples_outside_timed_regions": seen - len(sm),
+                "what": "nvidia-smi every 50 ms; only the samples inside the timed region of the headline step count"}
 
 
 # --------------------------------------------------------------------------- reference arms
@@ -334,8 +356,9 @@ def run_reference_arm(args, layers, shapes, tokens):
 def make_timer(stream, world, dev):
     import torch.distributed as dist
 
-    def timed(fn, steps, warmup, inner=1):
-        """ms per call of fn: `warmup` untimed calls, then steps * inner timed ones between events."""
+    def timed(fn, steps, warmup, inner=1, sampler=None):
+        """ms per call of fn: `warmup` untimed calls, then steps * inner timed ones between events.
+        With `sampler` the region's wall-clock bounds are registered with it."""
         with torch.cuda.stream(stream):
             for _ in range(warmup):
                 fn()
@@ -344,12 +367,15 @@ def make_timer(stream, world, dev):
                 dist.barrier()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            wall0 = time.time()
             e0.record(stream)
             for _ in range(steps * inner):
                 fn()
             e1.record(stream)
             stream.synchronize()
             torch.cuda.synchronize()
+            if sampler is not None:
+                sampler.window(wall0, time.time())
             if world > 1:
                 dist.barrier()
         ms = e0.elapsed_time(e1)
@@ -688,7 +714,7 @@ def main():
     if rank == 0:
         sampler.start()
     inner = args.inner if args.inner > 0 else inner_for(run_dev, args.steps)
-    ms_step = timed(run_dev, args.steps, args.warmup, inner)
+    ms_step = timed(run_dev, args.steps, args.warmup, inner, sampler if rank == 0 else None)
     ms_eager = timed(step_device, max(args.steps // 4, 3), 2) if graph is not None else ms_step
     pc_graph = None if args.no_graph else capture(step_per_call)
     ms_per_call = timed(pc_graph.replay if pc_graph is not None else step_per_call, args.steps, args.warmup, max(1, inner // 2))

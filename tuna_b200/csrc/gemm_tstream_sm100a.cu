@@ -5,27 +5,27 @@
 // is kept (weights are MMA operand A, tokens operand B, the accumulator is an o^T tile,
 // kernel.cu:2182-2192) and nothing else.
 //
-// The idea.  The packed layout stores an 8x8 weight tile as 32 bytes in mma A-fragment order
-// (test.py:58-65: byte j = row j/4, column pair j%4).  A 16-byte piece of it is 4 rows x 8
-// columns, and that is exactly what one thread supplies to two tcgen05.st of shape 16x256b:
-// lane (g, t) of a warp (g = lane/4, t = lane%4) takes the 16 bytes of row group g/2, rows
-// 4(g%2)..+3, 8-column tile t of a 32-column step (one 128-bit shared load; a quarter-warp
-// reads 128 contiguous bytes), turns them into 16 half2 by 16 table lookups and stores them
-// into tensor memory with two instructions.  No shuffles, no transposition: the dequantised
-// weights exist only in registers and tensor memory.  The price is a permutation that costs
-// nothing:
-//   * rows: tensor-memory lane l of a 32-lane quarter holds weight row 4*(l%8) + l/8 of the
-//     quarter's 32 rows (undone by the epilogue, which owns one lane per thread);
-//   * K: column c of a step's 16 tensor-memory columns holds the column pair
-//     k = 8*((c%8)/2) + 2*(c%2) + 4*(c/8) (+0, +1) of the step's 32, so the two 16-wide MMAs of
-//     a step see K positions kappa <-> k = 8*(kappa/4) + 4*u + kappa%4 (u = MMA index).  The
-//     activation producer writes x into shared memory in the same order (8-byte pieces), which
-//     is free because it has to re-tile x into 8x16-byte core matrices anyway.
+// The idea.  The packed layout stores an 8x8 weight tile as 32 bytes (test.py:58-65: byte j =
+// row j/4, column pair j%4), so the 8 columns of one row are one 32-bit word of the tile.  A
+// dequant thread owns one weight row = one tensor-memory lane: per 32-column step it reads the
+// row's four words (one per tile), turns their 16 bytes into 16 half2 by 16 table lookups and
+// writes them to 16 consecutive tensor-memory columns with one tcgen05.st (shape 32x32b).  K
+// stays in natural order, so the activations need no re-ordering at all: TMA writes x straight
+// into the 128-byte-swizzled K-major tiles the MMA's shared-memory descriptor reads.  The
+// dequantised weights exist only in registers and tensor memory.  (An earlier version used the
+// 16x256b store shape, whose fragment is exactly a 16-byte piece of the packed layout: no
+// row permutation to undo, but a K permutation that two extra warps had to apply to x through
+// shared memory, and a store shape that costs the tensor-memory write path a third more.)
+// Which row a lane holds is chosen for the shared-memory reads: lane 32q + l holds row
+// 8*rg + l%8 with rg = 8*(q/2) + q%2 + 2*(l/8), so the four row groups a warp reads at once
+// differ in bits 1-2 of rg - the bits the 128-byte swizzle XORs into the 16-byte chunk index -
+// and the warp's 32-bit reads are bank-conflict free.  The epilogue undoes it (one lane per thread).
 //
-// The packed weights are staged by TMA: one 2-D box per slot (16 row groups x 512 or 1024 bytes
-// = 128 rows x 128 or 256 columns, the matrix viewed as [m/8] x [k] 32-bit words) into an
-// mbarrier-tracked ring that takes all the shared memory left (about 110 KB in flight per SM
-// whatever the consumers are doing), out-of-range rows and columns zero-filled by the copy engine.  (A first version streamed the weights with
+// The packed weights are staged by TMA: per slot (16 row groups x 512 or 1024 bytes = 128 rows
+// x 128 or 256 columns) one 3-D box, or one 2-D box per step where the 3-D view does not exist
+// (k not a multiple of 32), into an mbarrier-tracked ring of [step][row group][128 bytes]
+// stages, 128-byte swizzled, that takes all the shared memory left; out-of-range rows and
+// columns are zero-filled by the copy engine.  (A first version streamed the weights with
 // ld.global into a per-lane register ring: 64 KB per SM at best, less whenever a warp was busy
 // converting, and the loaded HBM latency of ~2 us capped it near 3.3 TB/s.)
 //
@@ -33,18 +33,16 @@
 // thread.  Re-balancing registers between warpgroups with setmaxnreg made ptxas spill more,
 // not less, in this kernel):
 //   warp 0       MMA issue: tcgen05.mma (M=128, N=tile_tok, K=16, fp32 accumulate), A from tensor
-//                memory, B through a no-swizzle shared-memory descriptor, D in tensor memory.
+//                memory, B through a 128-byte-swizzle shared-memory descriptor, D in tensor memory.
 //                The warp stays converged and one elected lane issues (a lone diverged thread
 //                running this loop needed ~80 clocks per MMA instead of ~12); a slot is 8 or 16
 //                MMAs per wait and commit, because that fixed cost per slot is what limits it
-//   warps 1, 3   activation re-tiling (alternating units): natural order -> the MMAs'
-//                core-matrix order with the K permutation above (128-bit shared loads, 64-bit
-//                shared stores)
+//   warps 1, 3   idle (they only help to build the lookup table)
 //   warp 2       copy producer: TMA boxes of packed weights into the weight ring and of x (fp16
-//                [n,k], L2 resident) into a natural-order activation ring
+//                [n,k], L2 resident; one box per 64 columns) into the activation ring
 //   warps 4-7    epilogue: tcgen05.ld of the accumulator, fp32 scale by absmax, fp16 store,
 //                split-K partials and fix-up
-//   warps 8-23   dequant: ld.shared.v4 -> prmt + ld.shared table lookups -> tcgen05.st into the A
+//   warps 8-23   dequant: ld.shared.u32 -> prmt + ld.shared table lookups -> tcgen05.st into the A
 //                slots.  A warp handles rows 32q..+31 (q = its 32-lane quarter) and four
 //                32-column steps of a slot; with 128-column slots four groups of four warps
 //                convert four slots at once, with 256-column slots two groups of eight warps two.
@@ -108,7 +106,6 @@ constexpr int kTsMaxWStages = 16;     // weight ring: as many stages as shared m
 constexpr int kTsLutBytes = 256 * 128;    // byte -> half2 table: 256 entries, 32 copies (one per bank) of 4 bytes
 constexpr int kTsSmemTotal = 227 * 1024;             // static + dynamic shared memory of a CTA on sm_100
 constexpr int kTsSmemDynamic = kTsSmemTotal - 1024;  // the static part (barriers) stays below 1 KB
-constexpr int kTsEpilogueWarp0 = 4;   // the epilogue warps' quarters are 0..3 in order
 constexpr int kTsDequantWarp0 = 8;
 constexpr int kTsDequantWarps = 16;
 constexpr int kTsThreads = 32 * (kTsDequantWarp0 + kTsDequantWarps);
@@ -118,7 +115,7 @@ constexpr int kTsMaxSeq = 64;  // GEMMs of one launch (tuna_matmul_sequence)
 // One GEMM of a launch.  The two tensor maps are what the copy producer hands to TMA; everything
 // else is read by the epilogue warps and the cursors.
 struct __align__(64) TsGemm {
-    CUtensorMap map_q;   // packed weights as [m/8 row groups] x [k 32-bit words]
+    CUtensorMap map_q;   // packed weights: the 5-D view (w_mode 1), else the 3-D view if q3d, else [m/8 row groups] x [k 32-bit words]
     CUtensorMap map_x;   // activations as [n] x [k] fp16
     const float *absmax;
     __half *o;
@@ -127,7 +124,7 @@ struct __align__(64) TsGemm {
     int row_tiles;    // ceil(m / (128 RB))
     int unit0;        // index of its first unit in the launch's unit sequence
     int tile0;        // index of its first tile among the launch's tiles (arrival counters)
-    int pad_;
+    int q3d;          // map_q is the 3-D view (one copy per slot) rather than the 2-D one (one copy per step)
 };
 
 struct TsParams {
@@ -143,6 +140,7 @@ struct TsParams {
     int acc_cols;     // columns of one accumulator buffer
     int units;        // units of all the GEMMs
     int units_q, units_r;  // units = units_q * CTAs + units_r: the first units_r CTAs take units_q + 1
+    int w_mode;       // layout of the weight stages (the kernel's WMODE)
 };
 
 template <int MAXG>
@@ -208,8 +206,15 @@ struct TsCursor {
 };
 
 // STEPS: 32-column steps per slot (4 or 8).  MAXG: capacity of the launch's GEMM table (1 for a
-// single GEMM, kTsMaxSeq for a sequence).
-template <int N_TILE, int STEPS, int MAXG>
+// single GEMM, kTsMaxSeq for a sequence).  WMODE: layout of a weight stage (128-byte rows, 128-byte
+// swizzle), the same for all GEMMs of a launch:
+//   1  [32-row block][step pair][row group of the block][step of the pair]: one 5-D box per slot
+//      that reads global memory in runs of 256 contiguous bytes (m % 32 == 0 and k % 64 == 0);
+//      a warp's four row groups are consecutive and the swizzle separates them, so tensor-memory
+//      lane l holds row l of the 128;
+//   0  [step][row group]: one 3-D box per slot (k % 32 == 0; 128-byte runs, measured 8 % slower in
+//      the copy alone) or one 2-D box per step (any k); rows assigned to lanes by lane_row_group().
+template <int N_TILE, int STEPS, int MAXG, int WMODE>
 __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const __grid_constant__ TsLaunch<MAXG> L)
 {
     const TsParams &p = L.c;
@@ -218,20 +223,17 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     constexpr int kSlotBytes = 16 * kChunkK * 4;            // packed bytes of a slot: 16 row groups x 4 bytes per column
     constexpr int kHalves = STEPS / 4;                      // warps that share a quarter of a slot
     constexpr int kGroups = kTsDequantWarps / (4 * kHalves);  // slots converted at once
-    // One 16-wide MMA's activations ("B tile"): [K half][token/8][token%8][16 bytes].  The K halves
-    // lie kLbo apart and consecutive tiles kBTile apart; both carry 32 bytes of padding so that the
-    // permuting warp's 8-byte stores of a half-warp (2 tokens x 8 weight tiles = 2 K halves x 2
-    // steps x ...) fall into 16 different 8-byte bank pairs.
-    constexpr uint32_t kLbo = N_TILE * 16 + 32, kSbo = 128;
-    constexpr uint32_t kBTile = 2 * kLbo + 32;
-    constexpr uint32_t kXStageBytes = 2 * STEPS * kBTile;             // permuted chunk, as the MMAs read it
-    constexpr uint32_t kXNatBytes = N_TILE * kChunkK * 2;             // chunk as TMA delivers it: [token][kChunkK] fp16
-    constexpr int kXN = N_TILE == 16 ? 4 : (N_TILE == 32 ? 3 : 2);    // natural-order stages (TMA -> permuting warp)
-    constexpr int kXS = N_TILE == 16 ? 3 : 2;                         // permuted stages (permuting warp -> MMA)
-    static_assert(kXN <= kTsMaxXStages && kXS <= kTsMaxXStages, "barrier arrays too small");
-    static_assert(kLbo % 16 == 0 && kBTile % 16 == 0 && (kLbo % 128) == 32 && ((2 * kBTile) % 128) == 64, "operand tile padding");
+    // Activations of a unit: one tile of [token][64 columns] fp16 (128-byte rows, 128-byte swizzle,
+    // 8-token groups 1024 bytes apart) per 64 columns, as TMA writes it and the MMA descriptor reads it.
+    constexpr int kXTiles = kChunkK / 64;
+    constexpr uint32_t kXTileBytes = N_TILE * 128;
+    constexpr uint32_t kXStageBytes = kXTiles * kXTileBytes;
+    constexpr int kXS = N_TILE == 64 ? 3 : 4;                         // activation stages (TMA -> MMA)
+    constexpr uint32_t kStepBytes = 16 * 128;                         // one step of a weight stage: 16 row groups x 128 bytes
+    static_assert(kXS <= kTsMaxXStages, "barrier arrays too small");
+    static_assert(kXStageBytes % 1024 == 0 && kSlotBytes % 1024 == 0, "swizzle atoms are 1024 bytes");
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t bars[2 * kTsMaxASlots + 4 * kTsMaxXStages + 4 + 2 * kTsMaxWStages];
+    __shared__ __align__(8) uint64_t bars[2 * kTsMaxASlots + 2 * kTsMaxXStages + 4 + 2 * kTsMaxWStages];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
@@ -243,14 +245,17 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     // Let the next kernel in the stream become resident as SMs free up.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // Shared memory: the byte -> half2 table (32 KB: 256 entries x 32 bank copies), the two
-    // activation rings, and weight stages in everything that is left.
+    // Shared memory: the byte -> half2 table (32 KB: 256 entries x 32 bank copies), the
+    // activation ring, and weight stages in everything that is left (all 1024-byte aligned).
     const uint32_t dyn0 = smem_u32(smem);
     const uint32_t lut_addr = dyn0;
-    const uint32_t xnat = lut_addr + kTsLutBytes;
-    const uint32_t xring = xnat + kXN * kXNatBytes;
-    const uint32_t w0 = (xring + kXS * kXStageBytes + 1023u) & ~1023u;
+    const uint32_t xring = lut_addr + kTsLutBytes;
+    const uint32_t w0 = xring + kXS * kXStageBytes;
+#ifdef TS_WS_LIMIT  // timing experiment: fewer weight stages in flight
+    const int WS = min(TS_WS_LIMIT, (int)((dyn0 + kTsSmemDynamic - w0) / kSlotBytes));
+#else
     const int WS = min(kTsMaxWStages, (int)((dyn0 + kTsSmemDynamic - w0) / kSlotBytes));
+#endif
     auto w_stage = [&](int i) -> uint32_t { return w0 + (uint32_t)i * kSlotBytes; };
 
     const uint32_t bar0 = smem_u32(&bars[0]);
@@ -258,7 +263,6 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     const uint32_t x_full = a_empty + 8 * kTsMaxASlots, x_empty = x_full + 8 * kTsMaxXStages;
     const uint32_t d_full = x_empty + 8 * kTsMaxXStages, d_empty = d_full + 16;
     const uint32_t w_full = d_empty + 16, w_empty = w_full + 8 * kTsMaxWStages;
-    const uint32_t xn_full = w_empty + 8 * kTsMaxWStages, xn_empty = xn_full + 8 * kTsMaxXStages;
     volatile int *abort_flag = &s_abort;
 
     // this CTA's contiguous range of units
@@ -269,7 +273,6 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         s_abort = 0;
         for (int i = 0; i < kTsMaxASlots; ++i) { mbar_init(a_full + 8 * i, 4 * kHalves); mbar_init(a_empty + 8 * i, 1); }
         for (int i = 0; i < kTsMaxXStages; ++i) { mbar_init(x_full + 8 * i, 1); mbar_init(x_empty + 8 * i, 1); }
-        for (int i = 0; i < kTsMaxXStages; ++i) { mbar_init(xn_full + 8 * i, 1); mbar_init(xn_empty + 8 * i, 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(d_full + 8 * i, 1); mbar_init(d_empty + 8 * i, 4); }
         for (int i = 0; i < kTsMaxWStages; ++i) { mbar_init(w_full + 8 * i, 1); mbar_init(w_empty + 8 * i, 4 * kHalves); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -308,11 +311,12 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     if (warp == 0) {
         // ------------------------------------------------------------------ MMA issue
         // The warp stays converged: every lane runs the loop and the waits, one elected lane
-        // issues the MMAs and the commits.  Descriptors: the high word is constant, the low word
-        // is the operand address and the leading byte offset.
+        // issues the MMAs and the commits.  Descriptors (K-major, 128-byte swizzle): the high word
+        // is constant (8-token groups 1024 bytes apart, version 1, layout type 2), the low word is the
+        // start address; 16 columns further along K is 32 bytes further inside the 128-byte row.
         tmem = finish_prologue();
         constexpr uint32_t idesc = make_idesc(N_TILE);
-        constexpr uint32_t desc_hi = (kSbo >> 4) | (1u << 14);
+        constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
         Ring ra, rx, rd;
         TsCursor cur;
         cur.init(L, u_begin, n_units);
@@ -327,7 +331,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
             ok = __all_sync(0xffffffffu, ok) != 0;
             TS_PROF_END(1)
             if (!ok) break;
-            const uint32_t desc_lo0 = (((xring + (uint32_t)rx.idx * kXStageBytes) & 0x3FFFFu) >> 4) | ((kLbo >> 4) << 16);
+            const uint32_t desc_lo0 = ((xring + (uint32_t)rx.idx * kXStageBytes) & 0x3FFFFu) >> 4;
             const uint32_t dbase = tmem + (uint32_t)(rd.idx * p.acc_cols);
             for (int rb = 0; rb < RB; ++rb) {
                 TS_PROF_BEGIN
@@ -342,9 +346,9 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
 #ifdef TS_ABL_NOMMA  // timing experiment: commits only
                     for (int mm = 0; mm < 0; ++mm) {
 #else
-                    for (int mm = 0; mm < 2 * STEPS; ++mm) {  // step mm/2, 16-wide MMA mm%2
+                    for (int mm = 0; mm < 2 * STEPS; ++mm) {  // columns 16 mm .. 16 mm + 15 of the slot: 64-column tile mm/4
 #endif
-                        const uint64_t bdesc = ((uint64_t)desc_hi << 32) | (uint64_t)(desc_lo0 + mm * (kBTile >> 4));
+                        const uint64_t bdesc = ((uint64_t)desc_hi << 32) | (uint64_t)(desc_lo0 + (mm >> 2) * (kXTileBytes >> 4) + (mm & 3) * 2);
                         tc_mma_ts(dbase + (uint32_t)rb * N_TILE, abase + mm * 8, bdesc, idesc, (seg_first && mm == 0) ? 0u : 1u);
                     }
                     tc_commit(a_empty + 8 * ra.idx);
@@ -361,71 +365,15 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
             if (seg_last) rd.advance(2);
         }
     } else if (warp == 1 || warp == 3) {
-        // ------------------------------------------------------------------ activation re-tiling
-        // Two warps, alternating units.  Natural order ([token][column], as TMA delivers it) -> the
-        // MMAs' order: per step two operand tiles (u = 0, 1) of [K half][token/8][token%8][16 bytes],
-        // the 16 bytes of a token being the 8-byte column groups 4u .. 4u+3 of the 8-column weight
-        // tiles 2(K half), 2(K half)+1 of the step.  A lane moves one token's 16 bytes of one
-        // weight tile per trip: one 128-bit shared load (a quarter-warp reads 128 contiguous
-        // bytes), two 64-bit shared stores (conflict free thanks to the padding of kLbo and
-        // kBTile).  This costs the load/store unit a quarter of what the unit's table lookups
-        // cost; an earlier version that re-tiled straight from global memory with 8-byte cp.async
-        // cost as much as the lookups.
+        // ------------------------------------------------------------------ no role after the prologue
         tmem = finish_prologue();
-        const int me = warp >> 1;  // 0 or 1: takes the units me, me + 2, ...
-        int n_idx = me % kXN, x_idx = me % kXS;  // ring positions of unit u: u % kXN, u % kXS
-        uint32_t n_phase = 0, x_phase = 0;
-        const int tokq = lane >> 3, tt8 = lane & 7;
-        const uint32_t src_lane = (uint32_t)tokq * (kChunkK * 2) + (uint32_t)tt8 * 16;
-        const uint32_t dst_lane = (uint32_t)(2 * (tt8 >> 2)) * kBTile + (uint32_t)((tt8 >> 1) & 1) * kLbo + (uint32_t)(tt8 & 1) * 8 +
-                                  (uint32_t)(tokq & 1) * 16;  // + (token / 2 % 4) * 32 + (token / 8) * kSbo per trip
-        for (int u = me; u < n_units; u += 2) {
-            TS_PROF_BEGIN
-            bool ok = mbar_wait_warp(xn_full + 8 * n_idx, n_phase, abort_flag, p.status, 10);
-            ok = ok && mbar_wait_warp(x_empty + 8 * x_idx, x_phase ^ 1, abort_flag, p.status, 2);
-            TS_PROF_END(0)
-            if (!ok) break;
-            const uint32_t src0 = xnat + (uint32_t)n_idx * kXNatBytes + src_lane;
-            const uint32_t dst0 = xring + (uint32_t)x_idx * kXStageBytes + dst_lane;
-            // trips (tg, j): token 4 tg + tokq, weight tiles 8 j + tt8 (steps 2j, 2j+1); eight loads
-            // in flight, then their sixteen stores
-            constexpr int kTrips = (N_TILE / 4) * (STEPS / 2);
-#pragma unroll
-            for (int b0 = 0; b0 < kTrips; b0 += 8) {
-                uint4 v[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int tg = (b0 + i) / (STEPS / 2), j = (b0 + i) % (STEPS / 2);
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[i].x), "=r"(v[i].y), "=r"(v[i].z), "=r"(v[i].w) : "r"(src0 + (uint32_t)(4 * tg) * (kChunkK * 2) + (uint32_t)j * 128));
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int tg = (b0 + i) / (STEPS / 2), j = (b0 + i) % (STEPS / 2);
-                    // token 4 tg + tokq: row (4 tg + tokq) % 8 of 8-token group (4 tg + tokq) / 8
-                    const uint32_t d = dst0 + (uint32_t)(4 * j) * kBTile + (uint32_t)(tg >> 1) * kSbo + (uint32_t)((4 * tg) & 7) * 16 + (uint32_t)(tokq >> 1) * 32;
-                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(d), "r"(v[i].x), "r"(v[i].y) : "memory");
-                    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(d + kBTile), "r"(v[i].z), "r"(v[i].w) : "memory");
-                }
-            }
-            // generic-proxy writes -> visible to the tensor core's (async proxy) reads; the natural
-            // stage goes back to the copy warp (the arrival is a release, ordered after the loads)
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(x_full + 8 * x_idx);
-                mbar_arrive(xn_empty + 8 * n_idx);
-            }
-            n_idx += 2;
-            while (n_idx >= kXN) { n_idx -= kXN; n_phase ^= 1u; }
-            x_idx += 2;
-            while (x_idx >= kXS) { x_idx -= kXS; x_phase ^= 1u; }
-        }
     } else if (warp == 2) {
         // ------------------------------------------------------------------ copy producer
-        // One elected lane of the converged warp issues every TMA copy of the CTA: a box per slot
-        // (16 row groups x kChunkK 32-bit words of packed weights) into the weight ring, and a box
-        // per unit (tile_tok tokens x kChunkK columns of x, L2 resident; tokens past n and columns
-        // past k zero-filled) into the natural-order activation ring.  The weights are constants:
+        // One elected lane of the converged warp issues every TMA copy of the CTA: per slot the
+        // packed weights (16 row groups x kChunkK 32-bit words; one 3-D box, or one 2-D box per
+        // step) into the weight ring, and per unit kChunkK/64 boxes of x (tile_tok tokens x 64
+        // columns, L2 resident; tokens past n and columns past k zero-filled) into the activation
+        // ring, released by the MMAs' commit.  The weights are constants:
         // the first ring-full of their copies is issued before the dependency wait (and before
         // this warp joins the rest of the prologue); x may come from the kernel before this one.
         Ring rw, rn;
@@ -437,15 +385,18 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         auto issue_x = [&](bool blocking) {
             // as many activation copies as have a free stage (all the outstanding ones if `blocking`)
             while (ok && xu < n_units) {
-                if (blocking) ok = mbar_wait_warp(xn_empty + 8 * rn.idx, rn.phase ^ 1, abort_flag, p.status, 9);
-                else if (!(__all_sync(0xffffffffu, mbar_test_wait(xn_empty + 8 * rn.idx, rn.phase ^ 1)) != 0)) break;
+                if (blocking) ok = mbar_wait_warp(x_empty + 8 * rn.idx, rn.phase ^ 1, abort_flag, p.status, 9);
+                else if (!(__all_sync(0xffffffffu, mbar_test_wait(x_empty + 8 * rn.idx, rn.phase ^ 1)) != 0)) break;
                 if (!ok) break;
                 if (elect_one_sync()) {
-                    mbar_expect_tx(xn_full + 8 * rn.idx, kXNatBytes);
-                    tma_load_2d(xnat + (uint32_t)rn.idx * kXNatBytes, &L.g[xc.g].map_x, xc.chunk * kChunkK, p.tok0, xn_full + 8 * rn.idx);
+                    mbar_expect_tx(x_full + 8 * rn.idx, kXStageBytes);
+#pragma unroll
+                    for (int t = 0; t < kXTiles; ++t)
+                        tma_load_2d(xring + (uint32_t)rn.idx * kXStageBytes + (uint32_t)t * kXTileBytes, &L.g[xc.g].map_x,
+                                    xc.chunk * kChunkK + 64 * t, p.tok0, x_full + 8 * rn.idx);
                 }
                 __syncwarp();
-                rn.advance(kXN);
+                rn.advance(kXS);
                 ++xu;
                 xc.next(L);
             }
@@ -458,8 +409,18 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
                 TS_PROF_END(0)
                 if (!ok) break;
                 if (elect_one_sync()) {
+                    const TsGemm &G = L.g[wc.g];
                     mbar_expect_tx(w_full + 8 * rw.idx, kSlotBytes);
-                    tma_load_2d(w_stage(rw.idx), &L.g[wc.g].map_q, wc.chunk * kChunkK, (wc.tile * RB + w_rb) * 16, w_full + 8 * rw.idx);
+                    if (WMODE == 1) {
+                        tma_load_5d(w_stage(rw.idx), &G.map_q, 0, 0, 0, wc.chunk * (STEPS / 2), (wc.tile * RB + w_rb) * 4, w_full + 8 * rw.idx);
+                    } else if (G.q3d) {
+                        tma_load_3d(w_stage(rw.idx), &G.map_q, 0, (wc.tile * RB + w_rb) * 16, wc.chunk * STEPS, w_full + 8 * rw.idx);
+                    } else {
+#pragma unroll
+                        for (int st = 0; st < STEPS; ++st)
+                            tma_load_2d(w_stage(rw.idx) + (uint32_t)st * kStepBytes, &G.map_q, wc.chunk * kChunkK + 32 * st,
+                                        (wc.tile * RB + w_rb) * 16, w_full + 8 * rw.idx);
+                    }
                 }
                 __syncwarp();
                 rw.advance(WS);
@@ -476,7 +437,8 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     } else if (warp < kTsDequantWarp0) {
         // ------------------------------------------------------------------ epilogue
         tmem = finish_prologue();
-        const int row_in_block = 32 * quarter + 4 * (lane & 7) + (lane >> 3);
+        // the row this thread's lane holds
+        const int row_in_block = WMODE == 1 ? 32 * quarter + lane : 8 * lane_row_group(quarter, lane) + (lane & 7);
         const int tmem_lane = 32 * quarter + lane;
         const size_t slot_floats = (size_t)RB * kBlockRows * N_TILE;
         Ring rd;
@@ -593,13 +555,26 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         const int dq = warp - kTsDequantWarp0;
         const int half = (dq >> 2) % kHalves;      // which four steps of the slot
         const int group = dq / (4 * kHalves);
-        const int g = lane >> 2, t = lane & 3;
         tmem = finish_prologue();
         const uint32_t lane_key = lut_addr + (uint32_t)(lane * 4);  // this lane's copy of the table
         const uint32_t a_lane0 = tmem + ((uint32_t)(32 * quarter) << 16) + (uint32_t)p.a_base + 64u * (uint32_t)half;
-        // this lane's 16 bytes of its first step inside a stage: row group 4*quarter + g/2 (a row
-        // group is kChunkK*4 bytes), step 4*half (128 bytes per step), tile t, row half g%2
-        const uint32_t lane_soff = (uint32_t)(4 * quarter + (g >> 1)) * (uint32_t)(kChunkK * 4) + (uint32_t)half * 512u + (uint32_t)t * 32u + (uint32_t)(g & 1) * 16u;
+        // This thread's row inside a stage: word r%4 of 16-byte chunk 2 kt + r/4 of the 128-byte row
+        // of (row group, step), the chunk index XORed with (index of that 128-byte row in the stage) % 8.
+        //   WMODE 0: row index = 16 step + row group: offsets lane_soff[kt] + step * 2048;
+        //   WMODE 1: row index = ((quarter * STEPS/2 + step/2) * 4 + l/8) * 2 + step%2, whose low three
+        //            bits are 2 (l/8) + step%2: an odd step flips bit 0 of the chunk index (^ 16 bytes).
+        const int r = lane & 7;
+        const int rg = WMODE == 1 ? (lane >> 3) : lane_row_group(quarter, lane);
+        const uint32_t row0 = WMODE == 1 ? (uint32_t)((quarter * (STEPS / 2) + 2 * half) * 8 + 2 * rg) : (uint32_t)(64 * half + rg);
+        const uint32_t xor0 = WMODE == 1 ? (uint32_t)(2 * rg) : (uint32_t)(rg & 7);
+        uint32_t lane_soff[4];
+#pragma unroll
+        for (int kt = 0; kt < 4; ++kt)
+            lane_soff[kt] = row0 * 128u + (((uint32_t)(2 * kt + (r >> 2)) ^ xor0) << 4) + (uint32_t)(r & 3) * 4u;
+        auto w_addr = [&](uint32_t stage, int st, int kt) -> uint32_t {
+            if (WMODE == 1) return stage + (lane_soff[kt] ^ ((st & 1) ? 16u : 0u)) + (uint32_t)((st >> 1) * 1024 + (st & 1) * 128);
+            return stage + lane_soff[kt] + (uint32_t)st * kStepBytes;
+        };
         const int A = p.a_slots;
         int a_idx = group % A, w_idx = group % WS;  // ring positions of slot `sl`: sl % A, sl % WS
         uint32_t a_phase = (uint32_t)(group / A) & 1u, w_phase = (uint32_t)(group / WS) & 1u;
@@ -612,33 +587,37 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
             ok = mbar_wait_warp(w_full + 8 * w_idx, w_phase, abort_flag, p.status, 8);
             TS_PROF_END(3)
             if (!ok) break;
-            uint4 wv[4];
+            uint32_t wv[4][4];  // [step][tile]: the row's 8 columns of that tile
             {
-                const uint32_t src = w_stage(w_idx) + lane_soff;
+                const uint32_t src = w_stage(w_idx);
 #pragma unroll
                 for (int st = 0; st < 4; ++st)
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(wv[st].x), "=r"(wv[st].y), "=r"(wv[st].z), "=r"(wv[st].w) : "r"(src + st * 128));
+#pragma unroll
+                    for (int kt = 0; kt < 4; ++kt)
+#ifdef TS_ABL_LDS4  // timing experiment: a quarter of the weight loads
+                        if (kt > 0) wv[st][kt] = wv[st][0] + kt; else
+#endif
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(wv[st][kt]) : "r"(w_addr(src, st, kt)));
             }
             // software pipeline: the 16 lookups of step st + 1 are in flight while step st is stored
-            uint32_t v[2][4][4];
-            auto lookups = [&](const uint4 &wq, uint32_t (&o)[4][4]) {
-                const uint32_t w[4] = {wq.x, wq.y, wq.z, wq.w};  // word r = row 4(g%2)+r, byte c = column pair c
+            uint32_t v[2][16];
+            auto lookups = [&](const uint32_t (&w)[4], uint32_t (&o)[16]) {
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
+                for (int kt = 0; kt < 4; ++kt) {  // byte c of word kt = column pair c of tile kt
 #ifdef TS_ABL_NOLUT  // timing experiment: no table lookups
-                    o[r][0] = w[r]; o[r][1] = w[r] + lane_key; o[r][2] = w[r] ^ lane_key; o[r][3] = w[r] >> 1;
+                    o[4 * kt] = w[kt]; o[4 * kt + 1] = w[kt] + lane_key; o[4 * kt + 2] = w[kt] ^ lane_key; o[4 * kt + 3] = w[kt] >> 1;
 #else
-                    o[r][0] = ts_lookup(w[r], lane_key, 0x4440);
-                    o[r][1] = ts_lookup(w[r], lane_key, 0x4441);
-                    o[r][2] = ts_lookup(w[r], lane_key, 0x4442);
-                    o[r][3] = ts_lookup(w[r], lane_key, 0x4443);
+                    o[4 * kt] = ts_lookup(w[kt], lane_key, 0x4440);
+                    o[4 * kt + 1] = ts_lookup(w[kt], lane_key, 0x4441);
+                    o[4 * kt + 2] = ts_lookup(w[kt], lane_key, 0x4442);
+                    o[4 * kt + 3] = ts_lookup(w[kt], lane_key, 0x4443);
 #endif
                 }
             };
             lookups(wv[0], v[0]);
-            // All four shared loads of the stage have been issued and the first has returned (its
-            // data fed the lookups; they return in order): hand the stage back to the producer.  The
-            // arrival is a release: it is ordered after this warp's loads.
+            // All sixteen shared loads of the stage have been issued and the first have returned
+            // (their data fed the lookups; they return in order): hand the stage back to the
+            // producer.  The arrival is a release: it is ordered after this warp's loads.
             __syncwarp();
             if (lane == 0) mbar_arrive(w_empty + 8 * w_idx);
             TS_PROF_BEGIN
@@ -651,17 +630,11 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
 #pragma unroll
             for (int st = 0; st < 4; ++st) {
                 if (st < 3) lookups(wv[st + 1], v[(st + 1) & 1]);
-                uint32_t (&c)[4][4] = v[st & 1];
-                // rows 0, 1 -> lanes g, g+8; rows 2, 3 -> lanes g+16, g+24
+                uint32_t (&c)[16] = v[st & 1];
 #ifdef TS_ABL_NOST  // timing experiment: keep the lookups alive, skip the stores
-                asm volatile("" ::"r"(c[0][0] ^ c[0][1] ^ c[0][2] ^ c[0][3] ^ c[1][0] ^ c[1][1] ^ c[1][2] ^ c[1][3] ^ c[2][0] ^ c[2][1] ^ c[2][2] ^ c[2][3] ^ c[3][0] ^ c[3][1] ^ c[3][2] ^ c[3][3]), "r"(ta));
-#elif defined(TS_ABL_ST32)  // timing experiment (wrong layout): one 32-lane store per step instead of two 16-lane ones
-                asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(ta + 16u * st),
-                             "r"(c[0][0]), "r"(c[0][1]), "r"(c[0][2]), "r"(c[0][3]), "r"(c[1][0]), "r"(c[1][1]), "r"(c[1][2]), "r"(c[1][3]),
-                             "r"(c[2][0]), "r"(c[2][1]), "r"(c[2][2]), "r"(c[2][3]), "r"(c[3][0]), "r"(c[3][1]), "r"(c[3][2]), "r"(c[3][3]) : "memory");
+                asm volatile("" ::"r"(c[0] ^ c[1] ^ c[2] ^ c[3] ^ c[4] ^ c[5] ^ c[6] ^ c[7] ^ c[8] ^ c[9] ^ c[10] ^ c[11] ^ c[12] ^ c[13] ^ c[14] ^ c[15]), "r"(ta));
 #else
-                tc_st_16x256b_x2(ta + 16u * st, c[0][0], c[0][1], c[1][0], c[1][1], c[0][2], c[0][3], c[1][2], c[1][3]);
-                tc_st_16x256b_x2(ta + (16u << 16) + 16u * st, c[2][0], c[2][1], c[3][0], c[3][1], c[2][2], c[2][3], c[3][2], c[3][3]);
+                tc_st_x16(ta + 16u * st, c);  // columns 16 st .. + 15 of this warp's half slot = the step's 32 columns of K
 #endif
             }
             TS_PROF_END(1)
@@ -726,7 +699,7 @@ size_t gemm_tstream_workspace_bytes(int m, int n, int k, const tuna_config &c, i
     return partial_region_bytes(sm_count) + counters;
 }
 
-template <int N_TILE, int STEPS, int MAXG>
+template <int N_TILE, int STEPS, int MAXG, int WMODE>
 static int launch_ts(const TsLaunch<MAXG> &L, int ctas, cudaStream_t stream)
 {
     static bool attr_set[64] = {false};  // one-time, per device, opt-in to large dynamic shared memory
@@ -736,7 +709,7 @@ static int launch_ts(const TsLaunch<MAXG> &L, int ctas, cudaStream_t stream)
     {
         std::lock_guard<std::mutex> lock(mu);
         if (!attr_set[dev]) {
-            if (cudaFuncSetAttribute(gemm_w4a16_tstream_kernel<N_TILE, STEPS, MAXG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            if (cudaFuncSetAttribute(gemm_w4a16_tstream_kernel<N_TILE, STEPS, MAXG, WMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kTsSmemDynamic) != cudaSuccess)
                 return TUNA_ERR_NO_DEVICE;
             attr_set[dev] = true;
@@ -752,27 +725,35 @@ static int launch_ts(const TsLaunch<MAXG> &L, int ctas, cudaStream_t stream)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    return cudaLaunchKernelEx(&lc, gemm_w4a16_tstream_kernel<N_TILE, STEPS, MAXG>, L) == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
+    return cudaLaunchKernelEx(&lc, gemm_w4a16_tstream_kernel<N_TILE, STEPS, MAXG, WMODE>, L) == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
 }
 
 template <int MAXG>
 static int launch_ts_dispatch(const TsLaunch<MAXG> &L, int tile_tok, int steps, int ctas, cudaStream_t stream)
 {
-    switch (tile_tok * 10 + steps) {
-        case 164: return launch_ts<16, 4, MAXG>(L, ctas, stream);
-        case 168: return launch_ts<16, 8, MAXG>(L, ctas, stream);
-        case 324: return launch_ts<32, 4, MAXG>(L, ctas, stream);
-        case 328: return launch_ts<32, 8, MAXG>(L, ctas, stream);
-        case 644: return launch_ts<64, 4, MAXG>(L, ctas, stream);
-        case 648: return launch_ts<64, 8, MAXG>(L, ctas, stream);
+    switch (tile_tok * 100 + steps * 10 + L.c.w_mode) {
+        case 1640: return launch_ts<16, 4, MAXG, 0>(L, ctas, stream);
+        case 1641: return launch_ts<16, 4, MAXG, 1>(L, ctas, stream);
+        case 1680: return launch_ts<16, 8, MAXG, 0>(L, ctas, stream);
+        case 1681: return launch_ts<16, 8, MAXG, 1>(L, ctas, stream);
+        case 3240: return launch_ts<32, 4, MAXG, 0>(L, ctas, stream);
+        case 3241: return launch_ts<32, 4, MAXG, 1>(L, ctas, stream);
+        case 3280: return launch_ts<32, 8, MAXG, 0>(L, ctas, stream);
+        case 3281: return launch_ts<32, 8, MAXG, 1>(L, ctas, stream);
+        case 6440: return launch_ts<64, 4, MAXG, 0>(L, ctas, stream);
+        case 6441: return launch_ts<64, 4, MAXG, 1>(L, ctas, stream);
+        case 6480: return launch_ts<64, 8, MAXG, 0>(L, ctas, stream);
+        case 6481: return launch_ts<64, 8, MAXG, 1>(L, ctas, stream);
         default: return TUNA_ERR_BAD_CONFIG;
     }
 }
 
 // Fills the table entry of one GEMM (tensor maps, geometry); `unit0` / `tile0` are where its units
 // and tiles start in the launch.  Returns its unit count, or a negative status.
+static bool ts_wmode1_shape(int m, int k) { return m % 32 == 0 && k % 64 == 0; }
+
 static long long ts_fill_gemm(TsGemm *g, const void *q, const void *x, const float *absmax, void *o, int m, int n, int k,
-                              int row_blocks, int steps, int tile_tok, int unit0, int tile0)
+                              int row_blocks, int steps, int tile_tok, int unit0, int tile0, int w_mode)
 {
     const int chunk_k = 32 * steps;
     std::memset(g, 0, sizeof(*g));
@@ -782,14 +763,36 @@ static long long ts_fill_gemm(TsGemm *g, const void *q, const void *x, const flo
     g->row_tiles = div_up(m, kBlockRows * row_blocks);
     g->unit0 = unit0;
     g->tile0 = tile0;
-    // packed weights as [m/8 row groups] x [k 32-bit words] (a row group is 4k bytes); box = one slot:
-    // 16 row groups x chunk_k words.  Rows and columns past the matrix are zero-filled by the copy.
-    if (!make_tensor_map_2d(&g->map_q, CU_TENSOR_MAP_DATA_TYPE_UINT32, q, (uint64_t)k, (uint64_t)m / 8, (uint64_t)k * 4,
-                            (uint32_t)chunk_k, 16, CU_TENSOR_MAP_SWIZZLE_NONE))
+    // Packed weights (a row group is 4k bytes = k 32-bit words; word index = column index).  One
+    // step of a slot is a box of 16 row groups x 32 words (128 bytes), 128-byte swizzled.  Where k
+    // is a multiple of 32 the matrix also has the 3-D view [k/32 steps][m/8 row groups][32 words]
+    // (strides 128 bytes and 4k bytes) and a slot is one box of `steps` x 16 x 32; otherwise, or if
+    // the driver refuses that view, the 2-D view and one box per step.  Rows, columns and steps
+    // past the matrix are zero-filled by the copy.
+    // w_mode 1: 32-row blocks x pairs of steps, [m/32][k/64][4 row groups][2 steps][32 words] with
+    // strides 16k, 256, 4k and 128 bytes; a slot is one box of 4 x steps/2 x 4 x 2 x 32 words.
+    g->q3d = 0;
+    if (w_mode == 1) {
+        const uint64_t dims[5] = {32, 2, 4, (uint64_t)k / 64, (uint64_t)m / 32};
+        const uint64_t strides[4] = {128, (uint64_t)k * 4, 256, (uint64_t)k * 16};
+        const uint32_t box[5] = {32, 2, 4, (uint32_t)steps / 2, 4};
+        if (!ts_wmode1_shape(m, k) || !make_tensor_map_nd(&g->map_q, CU_TENSOR_MAP_DATA_TYPE_UINT32, q, 5, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return TUNA_ERR_BAD_CONFIG;
+    } else
+#ifdef TS_FORCE_Q2D  // timing experiment: one 2-D box per step even where the 3-D view exists
+    if (false &&
+#else
+    if (k % 32 == 0 &&
+#endif
+        make_tensor_map_3d(&g->map_q, CU_TENSOR_MAP_DATA_TYPE_UINT32, q, 32, (uint64_t)m / 8, (uint64_t)k / 32, (uint64_t)k * 4, 128,
+                           32, 16, (uint32_t)steps, CU_TENSOR_MAP_SWIZZLE_128B))
+        g->q3d = 1;
+    else if (!make_tensor_map_2d(&g->map_q, CU_TENSOR_MAP_DATA_TYPE_UINT32, q, (uint64_t)k, (uint64_t)m / 8, (uint64_t)k * 4, 32, 16,
+                                 CU_TENSOR_MAP_SWIZZLE_128B))
         return TUNA_ERR_NO_DEVICE;
-    // activations as [n tokens] x [k] fp16; box = one unit: tile_tok tokens x chunk_k columns
-    if (!make_tensor_map_2d(&g->map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, (uint64_t)k, (uint64_t)n, (uint64_t)k * 2,
-                            (uint32_t)chunk_k, (uint32_t)tile_tok, CU_TENSOR_MAP_SWIZZLE_NONE))
+    // activations as [n tokens] x [k] fp16; box = tile_tok tokens x 64 columns (128-byte rows, swizzled)
+    if (!make_tensor_map_2d(&g->map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x, (uint64_t)k, (uint64_t)n, (uint64_t)k * 2, 64,
+                            (uint32_t)tile_tok, CU_TENSOR_MAP_SWIZZLE_128B))
         return TUNA_ERR_NO_DEVICE;
     return (long long)g->row_tiles * g->chunks;
 }
@@ -817,7 +820,12 @@ int launch_gemm_tstream(const GemmArgs &a, const tuna_config &c)
     if (a.workspace == nullptr || a.workspace_bytes < gemm_tstream_workspace_bytes(a.m, a.n, a.k, c, a.sm_count))
         return TUNA_ERR_WORKSPACE;
     ts_fill_common(&L.c, c, steps, a.workspace, a.sm_count);
-    const long long units = ts_fill_gemm(&L.g[0], a.q, a.x, a.absmax, a.o, a.m, a.n, a.k, c.row_blocks, steps, c.tile_tok, 0, 0);
+    L.c.w_mode = ts_wmode1_shape(a.m, a.k) ? 1 : 0;
+    long long units = ts_fill_gemm(&L.g[0], a.q, a.x, a.absmax, a.o, a.m, a.n, a.k, c.row_blocks, steps, c.tile_tok, 0, 0, L.c.w_mode);
+    if (units == TUNA_ERR_BAD_CONFIG && L.c.w_mode == 1) {  // the driver refused the 5-D view
+        L.c.w_mode = 0;
+        units = ts_fill_gemm(&L.g[0], a.q, a.x, a.absmax, a.o, a.m, a.n, a.k, c.row_blocks, steps, c.tile_tok, 0, 0, 0);
+    }
     if (units < 0) return (int)units;
     if (units >= (1ll << 30)) return TUNA_ERR_TOO_LARGE;
     L.c.units = (int)units;
@@ -878,14 +886,28 @@ int launch_gemm_tstream_sequence(const tuna_gemm_desc *d, int count, const float
         L.c.count = cnt;
         L.c.status = status;
         ts_fill_common(&L.c, c, 8, workspace, sm_count);
+        // one stage layout per launch: the 256-byte-run one if every GEMM has it
+        L.c.w_mode = 1;
+        for (int i = 0; i < cnt; ++i)
+            if (!ts_wmode1_shape(d[first + i].m, d[first + i].k)) L.c.w_mode = 0;
         long long units = 0;
-        for (int i = 0; i < cnt; ++i) {
-            const tuna_gemm_desc &g = d[first + i];
-            const long long u = ts_fill_gemm(&L.g[i], g.q, g.x, (const float *)g.absmax, g.o, g.m, g.n, g.k, c.row_blocks, 8, c.tile_tok, (int)units, tile0);
-            if (u < 0) return (int)u;
-            units += u;
-            tile0 += L.g[i].row_tiles;
-            if (units >= (1ll << 30)) return TUNA_ERR_TOO_LARGE;
+        const int tile0_launch = tile0;
+        for (int attempt = 0; attempt < 2; ++attempt) {
+            units = 0;
+            tile0 = tile0_launch;
+            bool refused = false;
+            for (int i = 0; i < cnt; ++i) {
+                const tuna_gemm_desc &g = d[first + i];
+                const long long u = ts_fill_gemm(&L.g[i], g.q, g.x, (const float *)g.absmax, g.o, g.m, g.n, g.k, c.row_blocks, 8, c.tile_tok,
+                                                 (int)units, tile0, L.c.w_mode);
+                if (u == TUNA_ERR_BAD_CONFIG && L.c.w_mode == 1) { refused = true; break; }  // the driver refused the 5-D view
+                if (u < 0) return (int)u;
+                units += u;
+                tile0 += L.g[i].row_tiles;
+                if (units >= (1ll << 30)) return TUNA_ERR_TOO_LARGE;
+            }
+            if (!refused) break;
+            L.c.w_mode = 0;
         }
         L.c.units = (int)units;
         int ctas = c.ctas;

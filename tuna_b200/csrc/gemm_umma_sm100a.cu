@@ -72,20 +72,6 @@ struct UmmaParams {
     int dq_groups;
 };
 
-// Shared-memory matrix descriptor of a K-major operand tile stored with the 128-byte swizzle:
-// rows of 64 fp16 (128 bytes), 8-row groups 1024 bytes apart (stride byte offset), version 1,
-// layout type 2 (SWIZZLE_128B).  Advancing K by 16 elements adds 32 bytes to the start address.
-__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr)
-{
-    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-
-// Which weight row a TMEM lane holds.  Lane 32*quarter + l of a 128-row block takes row
-// 8*rg + (l & 7) with rg = 8*(quarter >> 1) + (quarter & 1) + 2*(l >> 3): the four row groups a
-// warp reads at once differ in bits 1-2 of rg, which is what the 128-byte swizzle XORs into
-// the 16-byte chunk index, so the warp's 32-bit reads of the staged bytes are bank-conflict free.
-__device__ __forceinline__ int lane_row_group(int quarter, int l) { return 8 * (quarter >> 1) + (quarter & 1) + 2 * (l >> 3); }
-
 struct UnitCursor {
     int tile, chunk;
     int left, total;  // units still to do / units of this CTA

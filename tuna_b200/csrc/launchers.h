@@ -39,6 +39,11 @@ DeviceStatus *device_status_word();
 int read_device_status(cudaStream_t stream);
 bool make_tensor_map_2d(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t inner, uint64_t outer,
                         uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle);
+bool make_tensor_map_3d(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
+                        uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
+                        CUtensorMapSwizzle swizzle);
+bool make_tensor_map_nd(CUtensorMap *map, CUtensorMapDataType dt, const void *base, int rank, const uint64_t *dims,
+                        const uint64_t *strides, const uint32_t *box, CUtensorMapSwizzle swizzle);
 
 cudaError_t launch_quantize(const void *w, const void *code, void *q, void *absmax, int m, int k, int sm_count,
                             cudaStream_t stream);

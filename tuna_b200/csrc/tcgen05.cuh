@@ -39,6 +39,18 @@ __device__ __forceinline__ void tc_st_x32(uint32_t taddr, const uint32_t (&v)[32
         : "memory");
 }
 
+// 32 lanes x 16 columns from 16 registers per thread: thread T supplies lane T, register i column i.
+__device__ __forceinline__ void tc_st_x16(uint32_t taddr, const uint32_t (&v)[16])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+
 __device__ __forceinline__ void tc_ld_x16(uint32_t taddr, float (&v)[16])
 {
     uint32_t r[16];
@@ -62,26 +74,19 @@ __host__ __device__ constexpr uint32_t make_idesc(int n_tile)
 }
 
 
-// 16 lanes x 16 columns of tensor memory from 8 registers per thread (shape 16x256b, two
-// repeats).  Thread T of the warp (g = T / 4, t = T % 4) supplies
-//   r0, r1: lane g,     columns 2t, 2t+1        r2, r3: lane g + 8, columns 2t, 2t+1
-//   r4, r5: lane g,     columns 8+2t, 8+2t+1    r6, r7: lane g + 8, columns 8+2t, 8+2t+1
-// relative to the lane and column of `taddr` (lane: the warp's 32-lane quarter, +0 or +16).
-__device__ __forceinline__ void tc_st_16x256b_x2(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3,
-                                                 uint32_t r4, uint32_t r5, uint32_t r6, uint32_t r7)
+// Shared-memory matrix descriptor of a K-major operand tile stored with the 128-byte swizzle:
+// rows of 64 fp16 (128 bytes), 8-row groups 1024 bytes apart (stride byte offset), version 1,
+// layout type 2 (SWIZZLE_128B).  Advancing K by 16 elements adds 32 bytes to the start address.
+__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr)
 {
-    asm volatile("tcgen05.st.sync.aligned.16x256b.x2.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(r4), "r"(r5), "r"(r6), "r"(r7)
-                 : "memory");
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// Shared-memory matrix descriptor of a K-major operand tile without swizzle: 8-row x 16-byte
-// core matrices of 128 contiguous bytes; `lbo` = byte distance between the two core matrices
-// along K of one 16-wide MMA, `sbo` = byte distance between 8-row groups.  Version 1 (sm_100).
-__device__ __forceinline__ uint64_t make_desc_noswizzle(uint32_t smem_addr, uint32_t lbo, uint32_t sbo)
-{
-    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
-           (1ull << 46);
-}
+// Which weight row a TMEM lane holds when a dequant thread owns one row.  Lane 32*quarter + l of
+// a 128-row block takes row 8*rg + (l & 7) with rg = 8*(quarter >> 1) + (quarter & 1) + 2*(l >> 3):
+// the four row groups a warp reads at once differ in bits 1-2 of rg, which is what the 128-byte
+// swizzle XORs into the 16-byte chunk index, so the warp's 32-bit reads of the staged bytes
+// ([row group][128 bytes], swizzled) are bank-conflict free.
+__device__ __forceinline__ int lane_row_group(int quarter, int l) { return 8 * (quarter >> 1) + (quarter & 1) + 2 * (l >> 3); }
 
 }  // namespace tuna

@@ -507,6 +507,7 @@ def main():
     ap.add_argument("--workload", default="mistral7b_mlp_m16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replay")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-fused", action="store_true", help="N > 1: skip the fused GEMM + reduce step (tuna_matmul_sequence_reduce)")
     ap.add_argument("--no-extras", action="store_true", help="skip the sub-records of the other BASELINE configurations")
     ap.add_argument("--layers", type=int, default=0, help="use only the first N layers (profiling captures); 0 = all")
     ap.add_argument("--inner", type=int, default=0, help="repeats of the step inside one timed step (0 = fill about a second)")
@@ -663,6 +664,25 @@ def main():
         if collectives and world > 1 and n_row:
             dist.all_reduce(o_rows)
 
+    # The same step with the K-split layers' sum fused into the launch (tuna_matmul_sequence_reduce):
+    # the epilogue stores finished rows into every rank's exchange buffer over NVLink while the
+    # weights stream, a small kernel per launch exchanges flags and adds the slabs; no collective.
+    fused, fused_note, o_fused = None, None, None
+    if world > 1 and n_row and not args.no_fused:
+        try:
+            o_fused = [[torch.empty_like(o) for o in outs] for outs in o_seq]
+            fg = [(x_dev[i], g["q"], g["s"], o_fused[li][i], g["m"], tokens, g["k"]) for li, per in enumerate(gemms) for i, g in enumerate(per)]
+            partial = [g["kind"] == "row" for per in gemms for g in per]
+            need = tuna_b200.ReduceSequence.exchange_bytes([(g[4], g[5], g[6]) for g in fg], world, partial)
+            exchange = tuna_b200.Exchange(need, dev, group=dist.group.WORLD)
+            fused = tuna_b200.ReduceSequence(fg, code, exchange, partial=partial)
+        except Exception as exc:  # e.g. no CUDA IPC between the ranks' processes: the collective path stays
+            fused, fused_note = None, f"{type(exc).__name__}: {exc}"
+        ok = torch.tensor([1 if fused is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)  # all ranks or none
+        if int(ok.item()) == 0:
+            fused = None
+
     # The same step GEMM by GEMM (tuna_matmul, one launch each): reported beside the headline
     def step_per_call(collectives=True):
         pending = []
@@ -719,9 +739,28 @@ def main():
     pc_graph = None if args.no_graph else capture(step_per_call)
     ms_per_call = timed(pc_graph.replay if pc_graph is not None else step_per_call, args.steps, args.warmup, max(1, inner // 2))
     ms_gemm_only = None
+    ms_fused, fused_err = None, None
     if world > 1:
         g2 = None if args.no_graph else capture(lambda: step_device(False))
         ms_gemm_only = timed(g2.replay if g2 is not None else (lambda: step_device(False)), args.steps, args.warmup, inner)
+        if fused is not None:
+            g3 = None if args.no_graph else capture(fused.run)
+            ms_fused = timed(g3.replay if g3 is not None else fused.run, args.steps, args.warmup, inner)
+            # the fused sums against the all-reduced ones (both sum fp16 partials; the order of the adds differs)
+            with torch.cuda.stream(stream):
+                step_device()
+                stream.synchronize()
+            worst = 0.0
+            r = 0
+            for li, per in enumerate(gemms):
+                for i, g in enumerate(per):
+                    if g["kind"] != "row":
+                        continue
+                    a, b = o_fused[li][i].float(), o_seq[li][i].float()
+                    worst = max(worst, float((a - b).abs().max() / b.abs().max().clamp_min(1e-6)))
+            fused_err = worst
+            if lib.tuna_check_device_status(stream.cuda_stream) != 0:
+                fused_err = float("inf")
     # the same host-buffer sequence captured once and replayed: the host only pays one graph launch per step
     e2e_graph, e2e_launch = None, "eager calls"
     if not args.no_graph:
@@ -762,6 +801,13 @@ def main():
             gathered = torch.empty((world * tokens, gemms[0][col]["m"]), dtype=torch.float16, device=dev)
             allgather_us = timed(lambda: dist.all_gather_into_tensor(gathered, o_dev[col]), 50, 10) * 1e3
     clocks = sampler.stop() if rank == 0 else None
+
+    # N > 1: the step is the faster of the two ways to sum the K-split layers (both are reported)
+    ms_allreduce = ms_step
+    reduce_kind = "NCCL all-reduce after the launch" if world > 1 else None
+    if ms_fused is not None and fused_err is not None and fused_err <= 1e-2 and ms_fused < ms_step:
+        ms_step = ms_fused
+        reduce_kind = "fused: peer stores from the GEMM epilogue + one reduce kernel per launch (tuna_matmul_sequence_reduce)"
 
     dom_bytes = alg_bytes(gd["m"], tokens, gd["k"])
     peak, peak_kind = measured_peak()
@@ -839,7 +885,7 @@ def main():
         "config": {
             "workload": args.workload, "tokens": tokens, "layers": layers,
             "gemms_per_layer": [{"kind": k_, "m": m, "k": k} for k_, m, k in shapes],
-            "parallelism": "single GPU" if world == 1 else f"tp{world}: one seeded weight set sharded by tuna_b200.sharding - column-parallel N-split + row-parallel K-split with NCCL all-reduce",
+            "parallelism": "single GPU" if world == 1 else f"tp{world}: one seeded weight set sharded by tuna_b200.sharding - column-parallel N-split + row-parallel K-split; sum of the K-split partials: {reduce_kind}",
             "l2": "inputs larger than L2: every layer has its own weights (%.2f GB per step per job)" % (total_bytes / 1e9),
             "launch": "CUDA graph replay" if graph is not None or not args.no_graph else "eager",
             "timed_region": f"{args.steps} steps x {inner} back-to-back replays of the step = {args.steps * inner * ms_step / 1e3:.2f} s; ms_per_step is per replay",
@@ -856,12 +902,15 @@ def main():
         "e2e": {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "inner_repeats": inner_e2e,
                 "how": "tuna_b200.HostSequence: pinned HOST activations and outputs of every GEMM, the step in 4 groups (copy-in of a group, launch of the previous one, copy-out of the one before on three streams); weights resident (they are parameters)", "launch": e2e_launch},
-        "gpu_launches": launches_per_step * args.steps * inner,
+        # the library's own kernels in the timed region (the fused step adds one reduce kernel per launch)
+        "gpu_launches": launches_per_step * (2 if ms_step is ms_fused else 1) * args.steps * inner,
         "clocks": clocks,
         "parity": parity,
     }
     if world > 1:
-        line["multi_gpu"] = {"gemm_only_ms_per_step": ms_gemm_only, "gemm_plus_allreduce_ms_per_step": ms_step,
+        line["multi_gpu"] = {"gemm_only_ms_per_step": ms_gemm_only, "gemm_plus_allreduce_ms_per_step": ms_allreduce,
+                             "fused_gemm_reduce_ms_per_step": ms_fused, "fused_vs_allreduce_max_rel_diff": fused_err,
+                             "fused_unavailable": fused_note, "step_uses": reduce_kind,
                              "gemm_only_gbs": total_bytes / (ms_gemm_only * 1e-3) / 1e9 if ms_gemm_only else None,
                              "allgather_us": allgather_us,
                              "note": "the K-split layers' partial outputs lie in one buffer and are summed by ONE all-reduce after the step's launch (per group of the sequence in the end-to-end path); the all-gather that would reassemble a column-parallel output is timed alone, it is not part of the MLP step"}

@@ -192,11 +192,50 @@ typedef struct tuna_gemm_desc {
     const void *absmax; /* fp32 [m]            */
     void *o;            /* fp16 [n, m]         */
     int32_t m, n, k;
-    int32_t reserved;
+    int32_t flags;      /* 0, or TUNA_GEMM_PARTIAL in a tuna_matmul_sequence_reduce call */
 } tuna_gemm_desc;
 int tuna_matmul_sequence(const tuna_gemm_desc *gemms, int count, const void *code, void *workspace, size_t workspace_bytes,
                          void *stream);
 size_t tuna_matmul_sequence_workspace_bytes(const tuna_gemm_desc *gemms, int count);
+
+/*
+ * K-split (row-parallel) GEMMs fused with the sum of their partial outputs over the GPUs of one
+ * node.  No counterpart in the reference (it has no multi-GPU path; a tensor-parallel caller runs
+ * its `matmul` per rank and all-reduces the fp16 outputs).  Every rank calls
+ * tuna_matmul_sequence_reduce with the same list of shapes, token counts (1..64) and flags; a GEMM
+ * with flags = TUNA_GEMM_PARTIAL gets this rank's K slice (q repacked for the slice, x columns of
+ * the slice) and, when the stream work is done, every rank's o holds the sum over ranks, added in
+ * rank order in fp32 (identical on all ranks); a GEMM with flags = 0 is an ordinary one that
+ * shares the launch (e.g. the column-parallel GEMMs of the same layers).  The GEMM kernel's epilogue stores finished rows straight into every rank's
+ * exchange buffer (peer memory, ordinary stores), a small kernel per launch raises this rank's
+ * flag on every peer, waits for all flags - at most about a second, then the device status word
+ * reports TUNA_ERR_DEVICE_TIMEOUT through tuna_check_device_status - and sums.  Two launches
+ * (GEMMs, reduce) per 64 GEMMs, capturable in a CUDA graph (the exchange number lives in device
+ * memory).  Calls on one exchange must be issued in the same order on every rank, on one stream
+ * per rank.
+ *   tuna_exchange_bytes    size every rank's buffer needs for the largest call it will make
+ *   tuna_exchange_create   allocates and zero-fills this rank's buffer (cudaMalloc) and returns
+ *                          a TUNA_IPC_HANDLE_BYTES-byte handle other processes can open
+ *   tuna_exchange_open     maps a peer's buffer from its handle (cudaIpcOpenMemHandle)
+ *   tuna_exchange_close / tuna_exchange_destroy   undo open / create
+ * tuna_exchange.buffer[] holds the buffers of all ranks in rank order (own buffer at [rank]);
+ * world = 1 is valid (the sum of one slab).
+ */
+#define TUNA_GEMM_PARTIAL 1 /* tuna_gemm_desc.flags: a K-split GEMM whose output is summed over the ranks */
+#define TUNA_MAX_PEERS 8
+#define TUNA_IPC_HANDLE_BYTES 64
+typedef struct tuna_exchange {
+    int32_t rank, world;
+    void *buffer[TUNA_MAX_PEERS];
+    size_t bytes; /* of each buffer */
+} tuna_exchange;
+size_t tuna_exchange_bytes(const tuna_gemm_desc *gemms, int count, int world);
+int tuna_exchange_create(size_t bytes, void **buffer, void *ipc_handle);
+int tuna_exchange_open(const void *ipc_handle, void **buffer);
+int tuna_exchange_close(void *peer_buffer);
+int tuna_exchange_destroy(void *buffer);
+int tuna_matmul_sequence_reduce(const tuna_gemm_desc *gemms, int count, const void *code, void *workspace, size_t workspace_bytes,
+                                const tuna_exchange *exchange, void *stream);
 
 /*
  * Quantizer: w fp16 [m, k] row-major -> packed codes q [m/8, k/8, 32] + absmax fp32 [m], for the

@@ -7,10 +7,10 @@ sm_100a kernels through the C ABI of libtuna_b200.so; there is no other
 implementation behind them.
 """
 
-from .ops import HostPipeline, HostSequence, MatmulSequence, dequant, matmul, matmul_batched, matmul_sequence, quantize, workspace_for, lookup_config  # noqa: F401
+from .ops import Exchange, HostPipeline, HostSequence, MatmulSequence, ReduceSequence, dequant, matmul, matmul_batched, matmul_sequence, quantize, workspace_for, lookup_config  # noqa: F401
 from ._lib import TunaConfig, TunaError, PATH_AUTO, PATH_STREAM, PATH_UMMA, PATH_TSTREAM  # noqa: F401
 
 __all__ = [
-    "matmul", "matmul_batched", "matmul_sequence", "MatmulSequence", "HostSequence", "dequant", "quantize", "HostPipeline", "workspace_for", "lookup_config",
+    "matmul", "matmul_batched", "matmul_sequence", "MatmulSequence", "ReduceSequence", "Exchange", "HostSequence", "dequant", "quantize", "HostPipeline", "workspace_for", "lookup_config",
     "TunaConfig", "TunaError", "PATH_AUTO", "PATH_STREAM", "PATH_UMMA", "PATH_TSTREAM",
 ]

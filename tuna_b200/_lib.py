@@ -37,12 +37,22 @@ class TunaGemmDesc(ctypes.Structure):
     """Mirror of `struct tuna_gemm_desc` (one GEMM of tuna_matmul_sequence)."""
 
     _fields_ = [("q", c_void_p), ("x", c_void_p), ("absmax", c_void_p), ("o", c_void_p),
-                ("m", c_int32), ("n", c_int32), ("k", c_int32), ("reserved", c_int32)]
+                ("m", c_int32), ("n", c_int32), ("k", c_int32), ("flags", c_int32)]
 
 
 PATH_AUTO, PATH_STREAM, PATH_UMMA, PATH_TSTREAM = 0, 1, 2, 3
 
 # every symbol include/tuna_b200.h declares: name -> (restype, argtypes)
+MAX_PEERS = 8
+GEMM_PARTIAL = 1
+IPC_HANDLE_BYTES = 64
+
+
+class TunaExchange(ctypes.Structure):
+    """`tuna_exchange` of include/tuna_b200.h: the exchange buffers of all ranks, in rank order."""
+    _fields_ = [("rank", ctypes.c_int32), ("world", ctypes.c_int32), ("buffer", c_void_p * MAX_PEERS), ("bytes", c_size_t)]
+
+
 SYMBOLS = {
     "tuna_matmul": (c_int, [c_void_p] * 5 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),
     "tuna_matmul_cfg": (c_int, [c_void_p] * 5 + [c_int] * 3 + [c_void_p, c_size_t, c_void_p, ctypes.POINTER(TunaConfig)]),
@@ -52,6 +62,13 @@ SYMBOLS = {
     "tuna_matmul_noalloc": (c_int, [c_void_p] * 5 + [c_int] * 3 + [c_void_p]),
     "tuna_matmul_sequence": (c_int, [ctypes.POINTER(TunaGemmDesc), c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
     "tuna_matmul_sequence_workspace_bytes": (c_size_t, [ctypes.POINTER(TunaGemmDesc), c_int]),
+    "tuna_matmul_sequence_reduce": (c_int, [ctypes.POINTER(TunaGemmDesc), c_int, c_void_p, c_void_p, c_size_t,
+                                            ctypes.POINTER(TunaExchange), c_void_p]),
+    "tuna_exchange_bytes": (c_size_t, [ctypes.POINTER(TunaGemmDesc), c_int, c_int]),
+    "tuna_exchange_create": (c_int, [c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
+    "tuna_exchange_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "tuna_exchange_close": (c_int, [c_void_p]),
+    "tuna_exchange_destroy": (c_int, [c_void_p]),
     "tuna_lookup_config": (c_int, [c_int] * 3 + [ctypes.POINTER(TunaConfig)]),
     "tuna_dequant": (c_int, [c_void_p] * 4 + [c_int] * 2 + [c_void_p]),
     "tuna_quantize": (c_int, [c_void_p] * 4 + [c_int] * 2 + [c_void_p]),

@@ -16,7 +16,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libtuna_b200.so"
-SOURCES = ["tuna_api.cu", "host_util.cu", "dequant_sm100a.cu", "quantize_sm100a.cu", "gemm_stream_sm100a.cu", "gemm_tstream_sm100a.cu", "gemm_umma_sm100a.cu", "ref_symbols.cu"]
+SOURCES = ["tuna_api.cu", "host_util.cu", "dequant_sm100a.cu", "quantize_sm100a.cu", "gemm_stream_sm100a.cu", "gemm_tstream_sm100a.cu", "gemm_umma_sm100a.cu", "exchange_sm100a.cu", "ref_symbols.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",

@@ -111,6 +111,7 @@ constexpr int kTsDequantWarps = 16;
 constexpr int kTsThreads = 32 * (kTsDequantWarp0 + kTsDequantWarps);
 
 constexpr int kTsMaxSeq = 64;  // GEMMs of one launch (tuna_matmul_sequence)
+constexpr int kMaxPeers = TUNA_MAX_PEERS;
 
 // One GEMM of a launch.  The two tensor maps are what the copy producer hands to TMA; everything
 // else is read by the epilogue warps and the cursors.
@@ -125,6 +126,7 @@ struct __align__(64) TsGemm {
     int unit0;        // index of its first unit in the launch's unit sequence
     int tile0;        // index of its first tile among the launch's tiles (arrival counters)
     int q3d;          // map_q is the 3-D view (one copy per slot) rather than the 2-D one (one copy per step)
+    long long slab_off;  // exchange launches: offset of this rank's slab for this GEMM inside a parity region, -1: none (o is written)
 };
 
 struct TsParams {
@@ -141,6 +143,13 @@ struct TsParams {
     int units;        // units of all the GEMMs
     int units_q, units_r;  // units = units_q * CTAs + units_r: the first units_r CTAs take units_q + 1
     int w_mode;       // layout of the weight stages (the kernel's WMODE)
+    // Exchange launches (K-split GEMMs whose partial outputs every rank sums): instead of o, a
+    // finished row goes to this rank's slab ([row][tile_tok] fp16) in the exchange buffer of every
+    // rank, with ordinary stores to peer memory; the reduce kernel that follows sums the slabs.
+    int n_peers;                 // 0: an ordinary launch
+    unsigned char *peer[kMaxPeers];
+    const unsigned int *epoch;   // exchanges completed so far on this rank (device counter): its parity selects the region
+    long long region0, region_bytes;  // offset of parity region 0 inside an exchange buffer, and the size of a region
 };
 
 template <int MAXG>
@@ -441,6 +450,32 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         const int row_in_block = WMODE == 1 ? 32 * quarter + lane : 8 * lane_row_group(quarter, lane) + (lane & 7);
         const int tmem_lane = 32 * quarter + lane;
         const size_t slot_floats = (size_t)RB * kBlockRows * N_TILE;
+        // exchange launches: where this launch's slabs start (the counter is read after the dependency wait)
+        long long region = 0;
+        if (p.n_peers > 0) region = p.region0 + (long long)((__ldcg(p.epoch) + 1u) & 1u) * p.region_bytes;
+        // 16 tokens (one accumulator piece) of one finished row, scaled: to o, or to every rank's slab
+        auto store_row = [&](const TsGemm &G, int row, int piece, const float (&v)[16], float sc) {
+            if (p.n_peers > 0 && G.slab_off >= 0) {
+                uint32_t h[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const __half2 t = __floats2half2_rn(v[2 * i] * sc, v[2 * i + 1] * sc);
+                    h[i] = *reinterpret_cast<const uint32_t *>(&t);
+                }
+                const long long off = region + G.slab_off + ((long long)row * N_TILE + piece * 16) * 2;
+                for (int pr = 0; pr < p.n_peers; ++pr) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(p.peer[pr] + off);
+                    dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+                    dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int tok = p.tok0 + piece * 16 + i;
+                    if (tok < G.n) G.o[(size_t)tok * G.m + row] = __float2half_rn(v[i] * sc);
+                }
+            }
+        };
         Ring rd;
         TsCursor cur;
         cur.init(L, u_begin, n_units);
@@ -465,13 +500,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
                     float v[16];
                     tc_ld_x16(tmem + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(rd.idx * p.acc_cols) + (uint32_t)rb * N_TILE + piece * 16, v);
                     if (full) {
-                        if (row < G.m) {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                const int tok = p.tok0 + piece * 16 + i;
-                                if (tok < G.n) G.o[(size_t)tok * G.m + row] = __float2half_rn(v[i] * sc);
-                            }
-                        }
+                        if (row < G.m) store_row(G, row, piece, v, sc);
                     } else {
                         // [rb][4-token group][128 lanes] float4: a warp store is 512 contiguous bytes
                         float4 *dst = reinterpret_cast<float4 *>(my_partial) + ((size_t)rb * (N_TILE / 4) + piece * 4) * kBlockRows + tmem_lane;
@@ -532,11 +561,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
                                     acc[4 * i] += a.x; acc[4 * i + 1] += a.y; acc[4 * i + 2] += a.z; acc[4 * i + 3] += a.w;
                                 }
                             }
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                const int tok = p.tok0 + piece * 16 + i;
-                                if (tok < G.n) G.o[(size_t)tok * G.m + row] = __float2half_rn(acc[i] * sc);
-                            }
+                            store_row(G, row, piece, acc, sc);
                         }
                     }
                 }
@@ -860,7 +885,7 @@ bool gemm_tstream_sequence_supported(const tuna_gemm_desc *d, int count)
 }
 
 int launch_gemm_tstream_sequence(const tuna_gemm_desc *d, int count, const float *code, void *workspace, size_t workspace_bytes,
-                                 int sm_count, cudaStream_t stream)
+                                 int sm_count, cudaStream_t stream, const tuna_exchange *ex)
 {
     if (workspace == nullptr || workspace_bytes < gemm_tstream_sequence_workspace_bytes(d, count, sm_count)) return TUNA_ERR_WORKSPACE;
     DeviceStatus *status = device_status_word();
@@ -886,6 +911,24 @@ int launch_gemm_tstream_sequence(const tuna_gemm_desc *d, int count, const float
         L.c.count = cnt;
         L.c.status = status;
         ts_fill_common(&L.c, c, 8, workspace, sm_count);
+        long long slab0[kTsMaxSeq];  // exchange launches: rank 0's slab of each GEMM inside a parity region
+        long long region_bytes = 0;
+        if (ex) {
+            region_bytes = (long long)((ex->bytes - kExHeaderBytes) / 2 / 256 * 256);
+            L.c.n_peers = ex->world;
+            for (int j = 0; j < ex->world; ++j) L.c.peer[j] = (unsigned char *)ex->buffer[j];
+            L.c.epoch = (const unsigned int *)ex->buffer[ex->rank];
+            L.c.region0 = kExHeaderBytes;
+            L.c.region_bytes = region_bytes;
+            long long off = 0;
+            for (int i = 0; i < cnt; ++i) {
+                slab0[i] = -1;
+                if (!(d[first + i].flags & TUNA_GEMM_PARTIAL)) continue;
+                slab0[i] = off;
+                off += (long long)ex->world * d[first + i].m * c.tile_tok * 2;
+            }
+            if (off > region_bytes) return TUNA_ERR_WORKSPACE;
+        }
         // one stage layout per launch: the 256-byte-run one if every GEMM has it
         L.c.w_mode = 1;
         for (int i = 0; i < cnt; ++i)
@@ -902,6 +945,7 @@ int launch_gemm_tstream_sequence(const tuna_gemm_desc *d, int count, const float
                                                  (int)units, tile0, L.c.w_mode);
                 if (u == TUNA_ERR_BAD_CONFIG && L.c.w_mode == 1) { refused = true; break; }  // the driver refused the 5-D view
                 if (u < 0) return (int)u;
+                if (ex) L.g[i].slab_off = slab0[i] < 0 ? -1 : slab0[i] + (long long)ex->rank * g.m * c.tile_tok * 2;
                 units += u;
                 tile0 += L.g[i].row_tiles;
                 if (units >= (1ll << 30)) return TUNA_ERR_TOO_LARGE;
@@ -914,7 +958,8 @@ int launch_gemm_tstream_sequence(const tuna_gemm_desc *d, int count, const float
         if (ctas > L.c.units) ctas = L.c.units;
         L.c.units_q = L.c.units / ctas;
         L.c.units_r = L.c.units % ctas;
-        const int st = launch_ts_dispatch(L, c.tile_tok, 8, ctas, stream);
+        int st = launch_ts_dispatch(L, c.tile_tok, 8, ctas, stream);
+        if (st == TUNA_OK && ex) st = launch_exchange_reduce(*ex, d + first, slab0, cnt, c.tile_tok, region_bytes, stream);
         if (st != TUNA_OK) return st;
     }
     return TUNA_OK;

@@ -70,7 +70,19 @@ int gemm_tstream_normalize_config(int m, int n, int k, int sm_count, tuna_config
 // The same kernel walking a table of independent GEMMs in one persistent launch (up to 64 per launch).
 bool gemm_tstream_sequence_supported(const tuna_gemm_desc *d, int count);
 size_t gemm_tstream_sequence_workspace_bytes(const tuna_gemm_desc *d, int count, int sm_count);
+// `ex` != nullptr: every GEMM is a K-split partial whose finished rows go to all ranks' exchange buffers,
+// and each launch is followed by the kernel that sums them into o (exchange_sm100a.cu).
 int launch_gemm_tstream_sequence(const tuna_gemm_desc *d, int count, const float *code, void *workspace, size_t workspace_bytes,
-                                 int sm_count, cudaStream_t stream);
+                                 int sm_count, cudaStream_t stream, const tuna_exchange *ex = nullptr);
+
+// Exchange buffers (layout in exchange_sm100a.cu): header, then two parity regions.
+constexpr int kExMaxPeers = TUNA_MAX_PEERS;
+constexpr int kExMaxItems = 64;          // GEMMs per launch, as in the sequence kernel
+constexpr int kExHeaderBytes = 4096;
+constexpr int kExFlag0Words = 64;        // flag of source rank j: 32-bit word 64 + 32 j of the header
+constexpr int kExFlagStrideWords = 32;
+size_t exchange_region_bytes(const tuna_gemm_desc *d, int count, int world);
+int launch_exchange_reduce(const tuna_exchange &ex, const tuna_gemm_desc *d, const long long *slab0_off, int count, int tile_tok,
+                           long long region_bytes, cudaStream_t stream);
 
 }  // namespace tuna

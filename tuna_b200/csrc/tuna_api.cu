@@ -221,6 +221,31 @@ extern "C" int tuna_matmul_sequence(const tuna_gemm_desc *g, int count, const vo
     return TUNA_OK;
 }
 
+extern "C" int tuna_matmul_sequence_reduce(const tuna_gemm_desc *g, int count, const void *code, void *workspace,
+                                           size_t workspace_bytes, const tuna_exchange *ex, void *stream)
+{
+    if (!g || !code || !ex) return TUNA_ERR_NULL_POINTER;
+    if (count < 1) return TUNA_ERR_BAD_SHAPE;
+    if (ex->world < 1 || ex->world > TUNA_MAX_PEERS || ex->rank < 0 || ex->rank >= ex->world) return TUNA_ERR_BAD_CONFIG;
+    for (int j = 0; j < ex->world; ++j) {
+        if (!ex->buffer[j]) return TUNA_ERR_NULL_POINTER;
+        if (!aligned(ex->buffer[j], 256)) return TUNA_ERR_MISALIGNED;
+    }
+    if (!aligned(code, 4) || !aligned(workspace, 16)) return TUNA_ERR_MISALIGNED;
+    // every rank must run the same launches: no entry is skipped here, so n = 0 is refused
+    for (int i = 0; i < count; ++i) {
+        const tuna_gemm_desc &d = g[i];
+        if (!d.q || !d.x || !d.absmax || !d.o) return TUNA_ERR_NULL_POINTER;
+        const int st = check_shape(d.m, d.n, d.k);
+        if (st != TUNA_OK) return st;
+        if (d.n > 64) return TUNA_ERR_TOO_LARGE;
+        if (!aligned(d.q, 16) || !aligned(d.x, 16) || !aligned(d.o, 16) || !aligned(d.absmax, 4)) return TUNA_ERR_MISALIGNED;
+    }
+    if (ex->bytes < tuna_exchange_bytes(g, count, ex->world)) return TUNA_ERR_WORKSPACE;
+    return launch_gemm_tstream_sequence(g, count, (const float *)code, workspace, workspace_bytes, device_sm_count(),
+                                        (cudaStream_t)stream, ex);
+}
+
 extern "C" int tuna_matmul(const void *q, const void *x, const void *code, const void *absmax, void *o,
                            int m, int n, int k, void *workspace, size_t workspace_bytes, void *stream)
 {

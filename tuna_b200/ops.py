@@ -161,6 +161,100 @@ class MatmulSequence:
                                                    self.workspace.numel() * self.workspace.element_size(), _stream_ptr(self.device)))
 
 
+class Exchange:
+    """The exchange buffers of a tensor-parallel group for `ReduceSequence` (`tuna_exchange`).
+
+    Every rank allocates one buffer of `nbytes` through the library (`tuna_exchange_create`), the
+    64-byte IPC handles travel through `torch.distributed` (`all_gather_object` on `group`, any
+    backend) and every rank maps its peers' buffers (`tuna_exchange_open`).  With `group=None` the
+    exchange has one rank (the sum of one slab): the same code path on a single GPU."""
+
+    def __init__(self, nbytes: int, device, group=None):
+        import ctypes
+
+        self.device = torch.device(device)
+        lib = _lib.load()
+        self._lib = lib
+        self.nbytes = int(nbytes)
+        self._local = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(_lib.IPC_HANDLE_BYTES)
+        with torch.cuda.device(self.device):
+            check(lib.tuna_exchange_create(self.nbytes, ctypes.byref(self._local), handle))
+        self.rank, self.world = 0, 1
+        self._peers = {}
+        handles = [handle.raw]
+        if group is not None:
+            import torch.distributed as dist
+
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+            if self.world > _lib.MAX_PEERS:
+                raise ValueError(f"at most {_lib.MAX_PEERS} ranks")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+        self.struct = _lib.TunaExchange()
+        self.struct.rank, self.struct.world, self.struct.bytes = self.rank, self.world, self.nbytes
+        with torch.cuda.device(self.device):
+            for j in range(self.world):
+                if j == self.rank:
+                    self.struct.buffer[j] = self._local.value
+                    continue
+                ptr = ctypes.c_void_p()
+                check(lib.tuna_exchange_open(handles[j], ctypes.byref(ptr)))
+                self._peers[j] = ptr
+                self.struct.buffer[j] = ptr.value
+        if group is not None:
+            dist.barrier(group=group)  # nobody launches before every mapping exists
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's (call it on every rank, after a barrier)."""
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for ptr in self._peers.values():
+                self._lib.tuna_exchange_close(ptr)
+            self._peers = {}
+            if self._local:
+                self._lib.tuna_exchange_destroy(self._local)
+                self._local = None
+
+
+class ReduceSequence(MatmulSequence):
+    """K-split GEMMs of a tensor-parallel group in one persistent launch, their partial outputs
+    summed over the ranks by the library (`tuna_matmul_sequence_reduce`) instead of a collective:
+    after `run()` every rank's `o` tensors hold the sum over ranks (added in rank order in fp32).
+    `gemms` as for `MatmulSequence` with this rank's K slice of q and x; every rank passes the same
+    shapes and token counts (1..64) in the same order.  `partial` (one bool per GEMM, default all
+    True) marks the K-split GEMMs; the others are ordinary GEMMs that share the launch (the
+    column-parallel GEMMs of the same layers).  `exchange` is an `Exchange` of at least
+    `ReduceSequence.exchange_bytes(shapes, world)` bytes."""
+
+    @staticmethod
+    def exchange_bytes(shapes, world: int, partial=None) -> int:
+        """Bytes every rank's exchange buffer needs for GEMMs of `shapes` = [(m, n, k), ...]."""
+        descs = (_lib.TunaGemmDesc * len(shapes))()
+        for i, (m, n, k) in enumerate(shapes):
+            descs[i] = _lib.TunaGemmDesc(0, 0, 0, 0, m, n, k, _lib.GEMM_PARTIAL if partial is None or partial[i] else 0)
+        return int(_lib.load().tuna_exchange_bytes(descs, len(shapes), world))
+
+    def __init__(self, gemms, c, exchange: Exchange, *, partial=None, workspace=None):
+        if any(g[5] < 1 or g[5] > 64 for g in gemms):
+            raise ValueError("token counts of a reduce sequence must be 1..64")
+        super().__init__(gemms, c, workspace=workspace)
+        for i in range(self.count):
+            self._descs[i].flags = _lib.GEMM_PARTIAL if partial is None or partial[i] else 0
+        self.exchange = exchange
+        need = self.exchange_bytes([(g[4], g[5], g[6]) for g in gemms], exchange.world, partial)
+        if exchange.nbytes < need:
+            raise ValueError(f"exchange buffers too small: {exchange.nbytes} < {need}")
+
+    def run(self) -> None:
+        import ctypes
+
+        with torch.cuda.device(self.device):
+            check(_lib.load().tuna_matmul_sequence_reduce(self._descs, self.count, self.code.data_ptr(), self.workspace.data_ptr(),
+                                                          self.workspace.numel() * self.workspace.element_size(),
+                                                          ctypes.byref(self.exchange.struct), _stream_ptr(self.device)))
+
+
 class HostSequence:
     """`MatmulSequence` for callers whose activations and outputs live in (pinned) HOST memory.
 

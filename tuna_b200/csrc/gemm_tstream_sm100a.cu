@@ -107,7 +107,10 @@ constexpr int kTsLutBytes = 256 * 128;    // byte -> half2 table: 256 entries, 3
 constexpr int kTsSmemTotal = 227 * 1024;             // static + dynamic shared memory of a CTA on sm_100
 constexpr int kTsSmemDynamic = kTsSmemTotal - 1024;  // the static part (barriers) stays below 1 KB
 constexpr int kTsDequantWarp0 = 8;
-constexpr int kTsDequantWarps = 16;
+#ifndef TS_DEQUANT_WARPS
+#define TS_DEQUANT_WARPS 16
+#endif
+constexpr int kTsDequantWarps = TS_DEQUANT_WARPS;
 constexpr int kTsThreads = 32 * (kTsDequantWarp0 + kTsDequantWarps);
 
 constexpr int kTsMaxSeq = 64;  // GEMMs of one launch (tuna_matmul_sequence)

@@ -2,9 +2,14 @@
 every case returns before the first CUDA call)."""
 
 import ctypes
+import os
+import socket
+
+import torch.distributed as dist
+import torch.multiprocessing as mp
 
 from tuna_b200 import _lib
-from tuna_b200.ops import ReduceSequence
+from tuna_b200.ops import Exchange, ReduceSequence
 
 
 def _descs(shapes, flags=None, ptr=0x1000):
@@ -52,3 +57,33 @@ def test_reduce_sequence_argument_checks():
     assert call(_descs([(256, 65, 256)]), 1, _exchange()) == -9  # one pass of the streaming kernel: at most 64 tokens
     assert call(_descs([(250, 16, 256)]), 1, _exchange()) == -2
     assert call(good, 1, _exchange(nbytes=4096 + 1024)) == -4    # exchange buffers too small for the call
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _exchange_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # rank 1 asks for a buffer smaller than the header: its creation fails whatever the machine
+        try:
+            Exchange((1 << 20) if rank == 0 else 16, "cuda:0", group=dist.group.WORLD)
+            ret[rank] = "created"
+        except RuntimeError as exc:
+            ret[rank] = str(exc)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_exchange_setup_fails_on_every_rank_together():
+    """One rank cannot create its buffer: no rank hangs in a collective, all raise."""
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_exchange_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert set(ret.keys()) == {0, 1}
+    assert all("could not allocate" in ret[r] for r in (0, 1)), dict(ret)

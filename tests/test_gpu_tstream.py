@@ -85,6 +85,34 @@ def test_tstream_token_tiles_and_passes(n, tile_tok, row_blocks, k_steps):
     _run(640, n, 520, seed=n, tile_tok=tile_tok, row_blocks=row_blocks, k_steps=k_steps)
 
 
+@pytest.mark.parametrize("k_steps", [4, 8])
+@pytest.mark.parametrize("m,n,k,tile_tok", [
+    (640, 64, 512, 64), (640, 33, 1024, 64), (1024, 32, 2048, 32),   # 5-D view (m % 32 = 0, k % 64 = 0), larger token tiles
+    (136, 16, 96, 16), (256, 16, 160, 16), (1032, 40, 2080, 64),     # 3-D view (k % 32 = 0 only): [step][row group] stages
+    (264, 16, 200, 16), (640, 64, 520, 64),                          # 2-D view, one box per step
+])
+def test_tstream_every_weight_stage_layout(m, n, k, tile_tok, k_steps):
+    _run(m, n, k, seed=m + n + k, tile_tok=tile_tok, row_blocks=1, k_steps=k_steps)
+
+
+@pytest.mark.parametrize("m,k", [(264, 200), (256, 160), (256, 256)])
+def test_tstream_one_hot_in_every_stage_layout(m, k):
+    """The one-hot check (exact weights back) for the three views of the packed matrix."""
+    n = 16
+    (x, q, absmax, code), _ = make_case(m, n, k, seed=5)
+    cols = np.linspace(0, k - 1, n).astype(np.int64)
+    x = np.zeros((n, k), dtype=np.float16)
+    x[np.arange(n), cols] = 1.0
+    dev = [torch.from_numpy(a).cuda() for a in (x, q, absmax, code)]
+    st, out, holder = run_matmul(dev, m, n, k, cfg=_lib.TunaConfig(path=_lib.PATH_TSTREAM, tile_tok=16))
+    assert st == 0
+    _status_ok()
+    w = orc.unpack_codes(q, m, k)
+    want = (code[w[:, cols]].astype(np.float16).astype(np.float32) * absmax[:, None]).astype(np.float16).T
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), want.view(np.uint16))
+    assert holder.guards_intact()
+
+
 @pytest.mark.parametrize("m,k", [(6144, 4096), (28672, 4096), (4096, 14336), (57344, 8192)])
 def test_tstream_benchmark_shapes_m16(m, k):
     n = 16

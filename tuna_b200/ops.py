@@ -177,44 +177,64 @@ class Exchange:
         self._lib = lib
         self.nbytes = int(nbytes)
         self._local = ctypes.c_void_p()
-        handle = ctypes.create_string_buffer(_lib.IPC_HANDLE_BYTES)
-        with torch.cuda.device(self.device):
-            check(lib.tuna_exchange_create(self.nbytes, ctypes.byref(self._local), handle))
-        self.rank, self.world = 0, 1
         self._peers = {}
-        handles = [handle.raw]
+        self.rank, self.world = 0, 1
+        dist = None
         if group is not None:
             import torch.distributed as dist
 
             self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
             if self.world > _lib.MAX_PEERS:
                 raise ValueError(f"at most {_lib.MAX_PEERS} ranks")
+        # A rank that fails still takes part in both collectives, so that all ranks raise together.
+        handle = ctypes.create_string_buffer(_lib.IPC_HANDLE_BYTES)
+        try:
+            with torch.cuda.device(self.device):
+                status = lib.tuna_exchange_create(self.nbytes, ctypes.byref(self._local), handle)
+        except Exception:  # no usable CUDA device in this process
+            status = -7
+        mine = handle.raw if status == 0 else None
+        handles = [mine]
+        if dist is not None:
             handles = [None] * self.world
-            dist.all_gather_object(handles, handle.raw, group=group)
+            dist.all_gather_object(handles, mine, group=group)
+        if any(h is None for h in handles):
+            self.close()
+            raise RuntimeError("exchange: a rank could not allocate or export its buffer" + (f" (this rank: status {status})" if status else ""))
         self.struct = _lib.TunaExchange()
         self.struct.rank, self.struct.world, self.struct.bytes = self.rank, self.world, self.nbytes
+        status = 0
         with torch.cuda.device(self.device):
             for j in range(self.world):
                 if j == self.rank:
                     self.struct.buffer[j] = self._local.value
                     continue
                 ptr = ctypes.c_void_p()
-                check(lib.tuna_exchange_open(handles[j], ctypes.byref(ptr)))
+                status = lib.tuna_exchange_open(handles[j], ctypes.byref(ptr))
+                if status != 0:
+                    break
                 self._peers[j] = ptr
                 self.struct.buffer[j] = ptr.value
-        if group is not None:
-            dist.barrier(group=group)  # nobody launches before every mapping exists
+        oks = [status == 0]
+        if dist is not None:
+            oks = [None] * self.world
+            dist.all_gather_object(oks, status == 0, group=group)  # also: nobody launches before every mapping exists
+        if not all(oks):
+            self.close()
+            raise RuntimeError("exchange: a rank could not map a peer's buffer" + (f" (this rank: status {status})" if status else ""))
 
     def close(self) -> None:
         """Unmaps the peers' buffers and frees this rank's (call it on every rank, after a barrier)."""
+        if not self._peers and (self._local is None or not self._local.value):
+            return
         with torch.cuda.device(self.device):
             torch.cuda.synchronize(self.device)
             for ptr in self._peers.values():
                 self._lib.tuna_exchange_close(ptr)
             self._peers = {}
-            if self._local:
+            if self._local is not None and self._local.value:
                 self._lib.tuna_exchange_destroy(self._local)
-                self._local = None
+            self._local = None
 
 
 class ReduceSequence(MatmulSequence):

@@ -700,7 +700,22 @@ def main():
     # group j-1's launch and group j-2's copy-out overlapping on three streams; the step ends when
     # the last output has reached the host
     x_host_l = [[x_host[i] for i, _ in enumerate(per)] for per in gemms]
-    o_host_l = [[torch.empty((tokens, g["m"]), dtype=torch.float16).pin_memory() for g in per] for per in gemms]
+    # host outputs: one pinned slab per pool (column-parallel / K-split outputs), the GEMMs' outputs back to
+    # back in it, so that HostSequence can return neighbouring outputs with one copy
+    slab_elems = {0: 0, 1: 0}
+    for per in gemms:
+        for g in per:
+            slab_elems[1 if g["kind"] == "row" else 0] += tokens * g["m"]
+    host_slab = {pid: torch.empty(max(n_, 1), dtype=torch.float16).pin_memory() for pid, n_ in slab_elems.items()}
+    used = {0: 0, 1: 0}
+    o_host_l = []
+    for per in gemms:
+        outs = []
+        for g in per:
+            pid = 1 if g["kind"] == "row" else 0
+            outs.append(host_slab[pid][used[pid]:used[pid] + tokens * g["m"]].view(tokens, g["m"]))
+            used[pid] += tokens * g["m"]
+        o_host_l.append(outs)
     host_gemms = [(x_host_l[li][i], g["q"], g["s"], o_host_l[li][i], g["m"], tokens, g["k"]) for li, per in enumerate(gemms) for i, g in enumerate(per)]
     pool_ids = [1 if g["kind"] == "row" else 0 for per in gemms for g in per]  # pool 1: outputs that need the all-reduce
 
@@ -708,7 +723,21 @@ def main():
         if 1 in pools:
             dist.all_reduce(pools[1])
 
-    hseq = tuna_b200.HostSequence(host_gemms, code, groups=4, after_group=reduce_rows if world > 1 else None, pool_ids=pool_ids)
+    hseq, e2e_reduce = None, ("NCCL all-reduce per group" if world > 1 else None)
+    if fused is not None:
+        try:  # the end-to-end step with the fused sum as well: its own exchange buffers, sized for a group's launch
+            exchange2 = tuna_b200.Exchange(exchange.nbytes, dev, group=dist.group.WORLD)
+            hseq = tuna_b200.HostSequence(host_gemms, code, groups=4, pool_ids=pool_ids, exchange=exchange2,
+                                          partial=[g["kind"] == "row" for per in gemms for g in per])
+            e2e_reduce = "fused (tuna_matmul_sequence_reduce per group)"
+        except Exception:
+            hseq = None
+        ok = torch.tensor([1 if hseq is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            hseq, e2e_reduce = None, "NCCL all-reduce per group"
+    if hseq is None:
+        hseq = tuna_b200.HostSequence(host_gemms, code, groups=4, after_group=reduce_rows if world > 1 else None, pool_ids=pool_ids)
 
     def step_e2e():
         hseq.run()
@@ -900,7 +929,7 @@ def main():
         "roofline_single_gemm": roofline_single,
         "cpu_baseline": cpu,
         "e2e": {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "inner_repeats": inner_e2e,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "inner_repeats": inner_e2e, "sum_of_k_split_partials": e2e_reduce,
                 "how": "tuna_b200.HostSequence: pinned HOST activations and outputs of every GEMM, the step in 4 groups (copy-in of a group, launch of the previous one, copy-out of the one before on three streams); weights resident (they are parameters)", "launch": e2e_launch},
         # the library's own kernels in the timed region (the fused step adds one reduce kernel per launch)
         "gpu_launches": launches_per_step * (2 if ms_step is ms_fused else 1) * args.steps * inner,

@@ -275,6 +275,30 @@ class ReduceSequence(MatmulSequence):
                                                           ctypes.byref(self.exchange.struct), _stream_ptr(self.device)))
 
 
+def _byte_span(first: torch.Tensor, nbytes: int) -> torch.Tensor:
+    """A uint8 view of `nbytes` bytes of `first`'s storage, starting where `first` starts."""
+    storage = first.untyped_storage()
+    offset = first.storage_offset() * first.element_size()
+    return torch.empty(0, dtype=torch.uint8, device=first.device).set_(storage, offset, (nbytes,))
+
+
+def _merge_copies(copies):
+    """[(dst, src), ...] contiguous tensors -> the same bytes as fewer, larger copies: runs whose
+    destinations follow one another in memory and whose sources do too (same storages) become one."""
+    runs = []
+    for dst, src in copies:
+        nbytes = dst.numel() * dst.element_size()
+        if runs:
+            d0, s0, n0 = runs[-1]
+            same = (d0.untyped_storage().data_ptr() == dst.untyped_storage().data_ptr()
+                    and s0.untyped_storage().data_ptr() == src.untyped_storage().data_ptr())
+            if same and d0.data_ptr() + n0 == dst.data_ptr() and s0.data_ptr() + n0 == src.data_ptr():
+                runs[-1] = (d0, s0, n0 + nbytes)
+                continue
+        runs.append((dst, src, nbytes))
+    return [(dst, src) if n == dst.numel() * dst.element_size() else (_byte_span(dst, n), _byte_span(src, n)) for dst, src, n in runs]
+
+
 class HostSequence:
     """`MatmulSequence` for callers whose activations and outputs live in (pinned) HOST memory.
 
@@ -288,14 +312,18 @@ class HostSequence:
     `after_group(pools)` (optional) runs on the compute stream between a group's launch and its
     copy-out; `pools` maps a pool id to ONE contiguous device tensor holding the outputs of the
     group's GEMMs with that id (`pool_ids`, one int per GEMM, default 0) - e.g. the K-split layers'
-    partial outputs, which one all-reduce then sums.  A `run()` can be captured into a CUDA graph
+    partial outputs, which one all-reduce then sums.  Host tensors that follow one another in one
+    pinned allocation travel as one copy per group and pool.  With `exchange` (an `Exchange`) the groups
+    run as `ReduceSequence`s: the GEMMs marked in `partial` (default all) are K slices whose outputs
+    come back summed over the ranks, without a collective.  A `run()` can be captured into a CUDA graph
     (the host buffers are then fixed addresses read and written at every replay)."""
 
-    def __init__(self, gemms, c, *, groups: int = 4, after_group=None, pool_ids=None):
+    def __init__(self, gemms, c, *, groups: int = 4, after_group=None, pool_ids=None, exchange=None, partial=None):
         if not gemms:
             raise ValueError("an empty sequence")
         self.device = gemms[0][1].device
         self.after_group = after_group
+        partial = list(partial) if partial is not None else None
         self.copy_in = torch.cuda.Stream(device=self.device)
         self.copy_out = torch.cuda.Stream(device=self.device)
         groups = max(1, min(int(groups), len(gemms)))
@@ -321,10 +349,18 @@ class HostSequence:
                 used[pid] += (n * m + 7) // 8 * 8
                 dev_gemms.append((xd, q, s_, od, m, n, k))
                 pairs.append((xh, xd, oh, od))
-            seq = MatmulSequence(dev_gemms, c, workspace=workspace)
+            if exchange is not None:  # the K-split GEMMs of the group are summed over the ranks inside the launch
+                seq = ReduceSequence(dev_gemms, c, exchange, partial=partial[bounds[j]:bounds[j + 1]] if partial is not None else None,
+                                     workspace=workspace)
+            else:
+                seq = MatmulSequence(dev_gemms, c, workspace=workspace)
             if workspace is None or seq.workspace.numel() > workspace.numel():
                 workspace = seq.workspace  # the groups run one after the other on one stream: one workspace
-            self._groups.append({"seq": seq, "pairs": pairs, "pools": slabs, "in": torch.cuda.Event(), "done": torch.cuda.Event(), "out": torch.cuda.Event()})
+            # copies of neighbouring tensors (adjacent in host memory AND on the device) are issued as one
+            by_pool = sorted(range(len(pairs)), key=lambda i: (ids[i], i))
+            self._groups.append({"seq": seq, "pairs": pairs, "pools": slabs, "in": torch.cuda.Event(), "done": torch.cuda.Event(), "out": torch.cuda.Event(),
+                                 "copies_in": _merge_copies([(pairs[i][1], pairs[i][0]) for i in range(len(pairs))]),
+                                 "copies_out": _merge_copies([(pairs[i][2], pairs[i][3]) for i in by_pool])})
         need = max(g["seq"].workspace.numel() for g in self._groups)
         if workspace.numel() < need:
             workspace = torch.zeros(need, dtype=torch.uint8, device=self.device)
@@ -342,8 +378,8 @@ class HostSequence:
         self.copy_out.wait_event(self._fork)
         for g in self._groups:
             with torch.cuda.stream(self.copy_in):
-                for xh, xd, _oh, _od in g["pairs"]:
-                    xd.copy_(xh, non_blocking=True)
+                for dst, src in g["copies_in"]:
+                    dst.copy_(src, non_blocking=True)
                 g["in"].record(self.copy_in)
             compute.wait_event(g["in"])
             g["seq"].run()
@@ -352,8 +388,8 @@ class HostSequence:
             g["done"].record(compute)
             self.copy_out.wait_event(g["done"])
             with torch.cuda.stream(self.copy_out):
-                for _xh, _xd, oh, od in g["pairs"]:
-                    oh.copy_(od, non_blocking=True)
+                for dst, src in g["copies_out"]:
+                    dst.copy_(src, non_blocking=True)
                 g["out"].record(self.copy_out)
         for g in self._groups:
             compute.wait_event(g["out"])

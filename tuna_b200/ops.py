@@ -349,21 +349,18 @@ class HostSequence:
                 used[pid] += (n * m + 7) // 8 * 8
                 dev_gemms.append((xd, q, s_, od, m, n, k))
                 pairs.append((xh, xd, oh, od))
+            # every group sizes its own workspace; the largest one then serves all (one stream, one after the other)
             if exchange is not None:  # the K-split GEMMs of the group are summed over the ranks inside the launch
-                seq = ReduceSequence(dev_gemms, c, exchange, partial=partial[bounds[j]:bounds[j + 1]] if partial is not None else None,
-                                     workspace=workspace)
+                seq = ReduceSequence(dev_gemms, c, exchange, partial=partial[bounds[j]:bounds[j + 1]] if partial is not None else None)
             else:
-                seq = MatmulSequence(dev_gemms, c, workspace=workspace)
+                seq = MatmulSequence(dev_gemms, c)
             if workspace is None or seq.workspace.numel() > workspace.numel():
-                workspace = seq.workspace  # the groups run one after the other on one stream: one workspace
+                workspace = seq.workspace
             # copies of neighbouring tensors (adjacent in host memory AND on the device) are issued as one
             by_pool = sorted(range(len(pairs)), key=lambda i: (ids[i], i))
             self._groups.append({"seq": seq, "pairs": pairs, "pools": slabs, "in": torch.cuda.Event(), "done": torch.cuda.Event(), "out": torch.cuda.Event(),
                                  "copies_in": _merge_copies([(pairs[i][1], pairs[i][0]) for i in range(len(pairs))]),
                                  "copies_out": _merge_copies([(pairs[i][2], pairs[i][3]) for i in by_pool])})
-        need = max(g["seq"].workspace.numel() for g in self._groups)
-        if workspace.numel() < need:
-            workspace = torch.zeros(need, dtype=torch.uint8, device=self.device)
         for g in self._groups:
             g["seq"].workspace = workspace
         self._fork = torch.cuda.Event()

@@ -217,7 +217,8 @@ size_t tuna_matmul_sequence_workspace_bytes(const tuna_gemm_desc *gemms, int cou
  *   tuna_exchange_create   allocates and zero-fills this rank's buffer (cudaMalloc) and returns
  *                          a TUNA_IPC_HANDLE_BYTES-byte handle other processes can open
  *   tuna_exchange_open     maps a peer's buffer from its handle (cudaIpcOpenMemHandle)
- *   tuna_exchange_close / tuna_exchange_destroy   undo open / create
+ *   tuna_exchange_close / tuna_exchange_destroy   undo open / create; a buffer may be destroyed only
+ *                          after every peer has closed its mapping of it
  * tuna_exchange.buffer[] holds the buffers of all ranks in rank order (own buffer at [rank]);
  * world = 1 is valid (the sum of one slab).
  */

@@ -178,6 +178,8 @@ class Exchange:
         self.nbytes = int(nbytes)
         self._local = ctypes.c_void_p()
         self._peers = {}
+        self._group = group
+        self._barrier_on_close = False  # set once every rank is known to hold a working exchange
         self.rank, self.world = 0, 1
         dist = None
         if group is not None:
@@ -220,21 +222,30 @@ class Exchange:
             oks = [None] * self.world
             dist.all_gather_object(oks, status == 0, group=group)  # also: nobody launches before every mapping exists
         if not all(oks):
+            self._barrier_on_close = True  # every rank takes this branch: unmap, meet, free
             self.close()
             raise RuntimeError("exchange: a rank could not map a peer's buffer" + (f" (this rank: status {status})" if status else ""))
+        self._barrier_on_close = True
 
     def close(self) -> None:
-        """Unmaps the peers' buffers and frees this rank's (call it on every rank, after a barrier)."""
-        if not self._peers and (self._local is None or not self._local.value):
-            return
-        with torch.cuda.device(self.device):
-            torch.cuda.synchronize(self.device)
-            for ptr in self._peers.values():
-                self._lib.tuna_exchange_close(ptr)
-            self._peers = {}
-            if self._local is not None and self._local.value:
+        """Unmaps the peers' buffers, waits for the other ranks to have done the same (a barrier on
+        the group: an exported buffer must outlive its mappings), then frees this rank's buffer.
+        Call it on every rank, with no launch on the exchange in flight."""
+        have_local = self._local is not None and bool(self._local.value)
+        if self._peers or have_local:
+            with torch.cuda.device(self.device):
+                torch.cuda.synchronize(self.device)
+                for ptr in self._peers.values():
+                    self._lib.tuna_exchange_close(ptr)
+        self._peers = {}
+        if self._group is not None and self._barrier_on_close:
+            import torch.distributed as dist
+
+            dist.barrier(group=self._group)
+        if have_local:
+            with torch.cuda.device(self.device):
                 self._lib.tuna_exchange_destroy(self._local)
-            self._local = None
+        self._local = None
 
 
 class ReduceSequence(MatmulSequence):

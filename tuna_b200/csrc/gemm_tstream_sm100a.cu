@@ -172,6 +172,17 @@ __device__ __forceinline__ uint32_t ts_lookup(uint32_t w, uint32_t lane_base, ui
     return v;
 }
 
+// The same lookup when the table lies at shared address 0x10000 with 256 bytes per entry: the
+// address 0x10000 + 256 * byte + 4 * lane is assembled by ONE prmt from `key` = 0x00010000 | 4 * lane
+// (bytes 0, 2, 3) and the selected byte of w (byte 1); `selector` = 0x7604 | (byte index << 4).
+__device__ __forceinline__ uint32_t ts_lookup256(uint32_t w, uint32_t key, uint32_t selector)
+{
+    uint32_t a, v;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(a) : "r"(w), "r"(key), "r"(selector));
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+
 // The CTA whose range holds unit u.
 __device__ __forceinline__ int ts_cta_of_unit(const TsParams &p, int u)
 {
@@ -240,9 +251,11 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     constexpr int kXTiles = kChunkK / 64;
     constexpr uint32_t kXTileBytes = N_TILE * 128;
     constexpr uint32_t kXStageBytes = kXTiles * kXTileBytes;
-    constexpr int kXS = N_TILE == 64 ? 3 : 4;                         // activation stages (TMA -> MMA)
+    // activation stages (TMA -> MMA); up to 32 tokens the ring has to fit below the lookup table (shared address 0x10000)
+    constexpr int kXS = (N_TILE == 64 || 4 * kXStageBytes + 4096 > 0x10000) ? 3 : 4;
     constexpr uint32_t kStepBytes = 16 * 128;                         // one step of a weight stage: 16 row groups x 128 bytes
     static_assert(kXS <= kTsMaxXStages, "barrier arrays too small");
+    static_assert(N_TILE == 64 || kXS * kXStageBytes + 4096 <= 0x10000, "the activation ring must end below the lookup table");
     static_assert(kXStageBytes % 1024 == 0 && kSlotBytes % 1024 == 0, "swizzle atoms are 1024 bytes");
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[2 * kTsMaxASlots + 2 * kTsMaxXStages + 4 + 2 * kTsMaxWStages];
@@ -257,18 +270,30 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     // Let the next kernel in the stream become resident as SMs free up.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // Shared memory: the byte -> half2 table (32 KB: 256 entries x 32 bank copies), the
-    // activation ring, and weight stages in everything that is left (all 1024-byte aligned).
+    // Shared memory (everything 1024-byte aligned): the byte -> half2 table (256 entries, one copy per
+    // bank), the activation ring, and weight stages in everything that is left.
+    //   kLut256 (token tiles up to 32): the table occupies shared addresses [0x10000, 0x20000) with 256
+    //   bytes per entry (half of them unused), which lets one prmt build a lookup's address; the
+    //   activation ring and the first weight stages lie below it, the other weight stages above.
+    //   Otherwise (64-token tiles need the room): 128 bytes per entry at the start of dynamic shared memory.
+    constexpr bool kLut256 = N_TILE <= 32;
     const uint32_t dyn0 = smem_u32(smem);
-    const uint32_t lut_addr = dyn0;
-    const uint32_t xring = lut_addr + kTsLutBytes;
-    const uint32_t w0 = xring + kXS * kXStageBytes;
+    const uint32_t smem_end = dyn0 + kTsSmemDynamic;
+    const uint32_t lut_addr = kLut256 ? 0x10000u : dyn0;
+    const uint32_t xring = kLut256 ? dyn0 : dyn0 + kTsLutBytes;
+    const uint32_t w_low = xring + kXS * kXStageBytes;                       // first weight stage
+    const int n_low = (kLut256 && w_low < 0x10000u) ? (int)((0x10000u - w_low) / kSlotBytes) : 0;   // weight stages below the table
+    const uint32_t w_high = kLut256 ? 0x20000u : w_low;
 #ifdef TS_WS_LIMIT  // timing experiment: fewer weight stages in flight
-    const int WS = min(TS_WS_LIMIT, (int)((dyn0 + kTsSmemDynamic - w0) / kSlotBytes));
+    const int WS = min(TS_WS_LIMIT, n_low + (int)((smem_end - w_high) / kSlotBytes));
 #else
-    const int WS = min(kTsMaxWStages, (int)((dyn0 + kTsSmemDynamic - w0) / kSlotBytes));
+    const int WS = min(kTsMaxWStages, n_low + (int)((smem_end - w_high) / kSlotBytes));
 #endif
-    auto w_stage = [&](int i) -> uint32_t { return w0 + (uint32_t)i * kSlotBytes; };
+    auto w_stage = [&](int i) -> uint32_t { return i < n_low ? w_low + (uint32_t)i * kSlotBytes : w_high + (uint32_t)(i - n_low) * kSlotBytes; };
+    if (kLut256 && dyn0 > 4096u) {  // the layout above assumes that dynamic shared memory starts within the first 4 KB
+        if (threadIdx.x == 0 && atomicCAS(&p.status->code, 0, 97) == 0) p.status->detail = (int)dyn0;
+        return;
+    }
 
     const uint32_t bar0 = smem_u32(&bars[0]);
     const uint32_t a_full = bar0, a_empty = a_full + 8 * kTsMaxASlots;
@@ -309,7 +334,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         const uint32_t ch = (uint32_t)__half_as_ushort(__float2half_rn(cv));
         for (int e = warp; e < 256; e += kTsThreads / 32) {
             const uint32_t v = __shfl_sync(0xffffffffu, ch, e >> 4) | (__shfl_sync(0xffffffffu, ch, e & 15) << 16);
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(lut_addr + (uint32_t)e * 128 + lane * 4), "r"(v) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(lut_addr + (uint32_t)e * (kLut256 ? 256 : 128) + lane * 4), "r"(v) : "memory");
         }
         asm volatile("griddepcontrol.wait;" ::: "memory");
         tc_fence_before();
@@ -584,7 +609,7 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
         const int half = (dq >> 2) % kHalves;      // which four steps of the slot
         const int group = dq / (4 * kHalves);
         tmem = finish_prologue();
-        const uint32_t lane_key = lut_addr + (uint32_t)(lane * 4);  // this lane's copy of the table
+        const uint32_t lane_key = lut_addr + (uint32_t)(lane * 4);  // this lane's copy of the table (kLut256: also the prmt's second operand)
         const uint32_t a_lane0 = tmem + ((uint32_t)(32 * quarter) << 16) + (uint32_t)p.a_base + 64u * (uint32_t)half;
         // This thread's row inside a stage: word r%4 of 16-byte chunk 2 kt + r/4 of the 128-byte row
         // of (row group, step), the chunk index XORed with (index of that 128-byte row in the stage) % 8.
@@ -635,10 +660,17 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
 #ifdef TS_ABL_NOLUT  // timing experiment: no table lookups
                     o[4 * kt] = w[kt]; o[4 * kt + 1] = w[kt] + lane_key; o[4 * kt + 2] = w[kt] ^ lane_key; o[4 * kt + 3] = w[kt] >> 1;
 #else
-                    o[4 * kt] = ts_lookup(w[kt], lane_key, 0x4440);
-                    o[4 * kt + 1] = ts_lookup(w[kt], lane_key, 0x4441);
-                    o[4 * kt + 2] = ts_lookup(w[kt], lane_key, 0x4442);
-                    o[4 * kt + 3] = ts_lookup(w[kt], lane_key, 0x4443);
+                    if (kLut256) {
+                        o[4 * kt] = ts_lookup256(w[kt], lane_key, 0x7604);
+                        o[4 * kt + 1] = ts_lookup256(w[kt], lane_key, 0x7614);
+                        o[4 * kt + 2] = ts_lookup256(w[kt], lane_key, 0x7624);
+                        o[4 * kt + 3] = ts_lookup256(w[kt], lane_key, 0x7634);
+                    } else {
+                        o[4 * kt] = ts_lookup(w[kt], lane_key, 0x4440);
+                        o[4 * kt + 1] = ts_lookup(w[kt], lane_key, 0x4441);
+                        o[4 * kt + 2] = ts_lookup(w[kt], lane_key, 0x4442);
+                        o[4 * kt + 3] = ts_lookup(w[kt], lane_key, 0x4443);
+                    }
 #endif
                 }
             };

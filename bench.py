@@ -953,10 +953,10 @@ def main():
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel: (bytes, where they come from).
 # The full-size launch (64 GEMMs, 2.9 GB) is too large to capture under `ncu --set full`; the figure is the
-# capture of the same kernel over 4 layers (8 GEMMs: 356.95 MB read + 9.5 MB written for 359.40 MB
+# capture of the same kernel over 4 layers (8 GEMMs: 356.87 MB read + 8.1 MB written for 359.40 MB
 # algorithmic), scaled by the layers - traffic grows in proportion, every layer has its own weights.
 DRAM_TRAFFIC_PER_LAUNCH: dict = {
-    ("sequence", "mistral7b_mlp_m16", 1): (8 * (356.95e6 + 9.51e6), "ncu capture of `python bench.py --layers 4 --steps 1 --warmup 3 "
+    ("sequence", "mistral7b_mlp_m16", 1): (8 * (356.87e6 + 8.14e6), "ncu capture of `python bench.py --layers 4 --steps 1 --warmup 3 "
                                             "--no-cpu-baseline --no-extras --inner 1` (one sequence launch), scaled x8 to the 32 layers"),
 }
 

@@ -334,7 +334,7 @@ def run_reference_arm(args, layers, shapes, tokens):
                     config={"workload": args.workload, "tokens": tokens, "layers": layers,
                             "step": "the full workload on ONE GPU (the reference cannot shard: unknown shapes are silent no-ops)",
                             "timing": "CUDA events, eager launches through the reference's wrapper(), output zero-fill included",
-                            "kind": "reference: /root/reference kernel.cu compiled for sm_100 into oracle/_ref (A6000-tuned table, mma.sync)"},
+                            "kind": "reference: its own kernel.cu compiled for sm_100 into oracle/_ref (A6000-tuned table, mma.sync)"},
                     e2e={"value": total / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
                          "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                          "how": "per GEMM: pinned-host x -> device, zero-fill o, wrapper(), o -> pinned host, one stream"},

@@ -52,7 +52,7 @@ __device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v)
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// grid (blocks per item, items).  Every block signals nothing but block (0, 0); every block waits.
+// grid (blocks per item, items).  Block (0, 0) signals; every block waits for all the flags itself.
 __global__ void __launch_bounds__(256) exchange_reduce_kernel(const __grid_constant__ ReduceLaunch R)
 {
     unsigned int *hdr = reinterpret_cast<unsigned int *>(R.local);
@@ -171,7 +171,18 @@ int launch_exchange_reduce(const tuna_exchange &ex, const tuna_gemm_desc *d, con
     }
     R.count = items;
     // A launch without partial GEMMs still runs the exchange (flags, number): every rank's launches stay in step.
-    const dim3 grid(4, (unsigned)(items > 0 ? items : 1));
+    // one thread per (row, 8 tokens) where that still fills the GPU: the slabs are read once, at HBM speed
+    int max_work = 1;
+    for (int i = 0; i < items; ++i) {
+        const int w = R.item[i].m * (tile_tok / 8);
+        max_work = w > max_work ? w : max_work;
+    }
+    int blocks_x = (max_work + 255) / 256;
+    if (blocks_x > 32) blocks_x = 32;
+    const dim3 grid((unsigned)blocks_x, (unsigned)(items > 0 ? items : 1));
+    // an ordinary launch: it starts when the GEMM kernel before it has completed (its stores, the remote
+    // ones included, are then performed); launching it and its successor programmatically early was
+    // measured and gained nothing
     exchange_reduce_kernel<<<grid, 256, 0, stream>>>(R);
     return cudaGetLastError() == cudaSuccess ? TUNA_OK : TUNA_ERR_LAUNCH;
 }

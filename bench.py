@@ -699,7 +699,18 @@ def main():
     # there, through the package's host-buffer API: the sequence in 4 groups, group j's copy-in,
     # group j-1's launch and group j-2's copy-out overlapping on three streams; the step ends when
     # the last output has reached the host
-    x_host_l = [[x_host[i] for i, _ in enumerate(per)] for per in gemms]
+    # host activations: every GEMM has its own buffer (a copy of its shape's activations), all of them back to
+    # back in one pinned slab in GEMM order, so that HostSequence can bring in a group with one copy
+    x_slab_host = torch.empty(layers * sum(t.numel() for t in x_host), dtype=torch.float16).pin_memory()
+    x_host_l, pos = [], 0
+    for per in gemms:
+        row = []
+        for i, _ in enumerate(per):
+            v = x_slab_host[pos:pos + x_host[i].numel()].view_as(x_host[i])
+            v.copy_(x_host[i])
+            pos += x_host[i].numel()
+            row.append(v)
+        x_host_l.append(row)
     # host outputs: one pinned slab per pool (column-parallel / K-split outputs), the GEMMs' outputs back to
     # back in it, so that HostSequence can return neighbouring outputs with one copy
     slab_elems = {0: 0, 1: 0}

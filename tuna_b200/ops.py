@@ -351,11 +351,15 @@ class HostSequence:
                 sizes[pid] = sizes.get(pid, 0) + (n * m + 7) // 8 * 8
             slabs = {pid: torch.empty(sz, dtype=torch.float16, device=self.device) for pid, sz in sizes.items()}
             used = {pid: 0 for pid in sizes}
+            # the group's activations also lie back to back on the device (16-byte aligned pieces)
+            x_slab = torch.empty(sum((n * k + 7) // 8 * 8 for (_xh, _q, _s, _oh, _m, n, k) in part), dtype=torch.float16, device=self.device)
+            x_used = 0
             dev_gemms, pairs = [], []
             for (xh, q, s_, oh, m, n, k), pid in zip(part, ids):
                 if not (xh.is_pinned() and oh.is_pinned()):
                     raise ValueError("HostSequence needs pinned host tensors (pageable copies would serialise)")
-                xd = torch.empty((n, k), dtype=torch.float16, device=self.device)
+                xd = x_slab[x_used:x_used + n * k].view(n, k)
+                x_used += (n * k + 7) // 8 * 8
                 od = slabs[pid][used[pid]:used[pid] + n * m].view(n, m)
                 used[pid] += (n * m + 7) // 8 * 8
                 dev_gemms.append((xd, q, s_, od, m, n, k))

@@ -507,6 +507,7 @@ def main():
     ap.add_argument("--workload", default="mistral7b_mlp_m16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replay")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-groups", type=int, default=4, help="groups the end-to-end step is cut into (copy-in / launch / copy-out pipeline)")
     ap.add_argument("--no-fused", action="store_true", help="N > 1: skip the fused GEMM + reduce step (tuna_matmul_sequence_reduce)")
     ap.add_argument("--no-extras", action="store_true", help="skip the sub-records of the other BASELINE configurations")
     ap.add_argument("--layers", type=int, default=0, help="use only the first N layers (profiling captures); 0 = all")
@@ -738,7 +739,7 @@ def main():
     if fused is not None:
         try:  # the end-to-end step with the fused sum as well: its own exchange buffers, sized for a group's launch
             exchange2 = tuna_b200.Exchange(exchange.nbytes, dev, group=dist.group.WORLD)
-            hseq = tuna_b200.HostSequence(host_gemms, code, groups=4, pool_ids=pool_ids, exchange=exchange2,
+            hseq = tuna_b200.HostSequence(host_gemms, code, groups=args.e2e_groups, pool_ids=pool_ids, exchange=exchange2,
                                           partial=[g["kind"] == "row" for per in gemms for g in per])
             e2e_reduce = "fused (tuna_matmul_sequence_reduce per group)"
         except Exception:
@@ -748,7 +749,7 @@ def main():
         if int(ok.item()) == 0:
             hseq, e2e_reduce = None, "NCCL all-reduce per group"
     if hseq is None:
-        hseq = tuna_b200.HostSequence(host_gemms, code, groups=4, after_group=reduce_rows if world > 1 else None, pool_ids=pool_ids)
+        hseq = tuna_b200.HostSequence(host_gemms, code, groups=args.e2e_groups, after_group=reduce_rows if world > 1 else None, pool_ids=pool_ids)
 
     def step_e2e():
         hseq.run()
@@ -941,7 +942,7 @@ def main():
         "cpu_baseline": cpu,
         "e2e": {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "inner_repeats": inner_e2e, "sum_of_k_split_partials": e2e_reduce,
-                "how": "tuna_b200.HostSequence: pinned HOST activations and outputs of every GEMM, the step in 4 groups (copy-in of a group, launch of the previous one, copy-out of the one before on three streams); weights resident (they are parameters)", "launch": e2e_launch},
+                "how": "tuna_b200.HostSequence: pinned HOST activations and outputs of every GEMM, the step in %d groups (copy-in of a group, launch of the previous one, copy-out of the one before on three streams)" % args.e2e_groups + "; weights resident (they are parameters)", "launch": e2e_launch},
         # the library's own kernels in the timed region (the fused step adds one reduce kernel per launch)
         "gpu_launches": launches_per_step * (2 if ms_step is ms_fused else 1) * args.steps * inner,
         "clocks": clocks,

@@ -4,8 +4,8 @@ One GPU: an exchange of one rank runs the whole path (slabs, parity regions, fla
 and must give the bits of the ordinary sequence launch.  Two GPUs: two processes (gloo carries the
 IPC handles), each with its K slice of one seeded weight set; every rank's result must equal the
 oracle on the full K within the GEMM tolerance and the two ranks' results must be the same bits.
-No test here makes a wait run out across GPUs: the bounded wait is the one exercised by
-`tuna_selftest_bounded_wait`'s test.
+The reduce kernel's bounded wait is made to run out on ONE GPU (a second rank that does not exist:
+a flag that nothing sets); no test makes a wait run out across GPUs.
 """
 
 import os
@@ -95,6 +95,44 @@ def test_exchange_validation():
     small.close()
     ex.close()
     assert lib.tuna_exchange_bytes(None, 1, 2) == 0
+
+
+def test_a_peer_that_never_signals_ends_in_a_status_not_a_hang():
+    """Rank 0 of a two-rank exchange whose rank 1 does not exist (its buffer is a second local one that
+    nobody signals): the reduce kernel's wait runs out after about a second, the device status word
+    reports it, the outputs stay untouched and the device keeps working."""
+    import ctypes
+    import time
+
+    lib = tuna_b200._lib.load()
+    shapes = [(256, 16, 512)]
+    _, gemms, refs, code = _gemms(shapes, 520)
+    need = tuna_b200.ReduceSequence.exchange_bytes(shapes, 2)
+    mine, silent = tuna_b200.Exchange(need, "cuda"), tuna_b200.Exchange(need, "cuda")
+
+    class TwoRanks:  # the exchange as rank 0 of 2 sees it
+        rank, world, nbytes = 0, 2, need
+        struct = tuna_b200._lib.TunaExchange()
+
+    TwoRanks.struct.rank, TwoRanks.struct.world, TwoRanks.struct.bytes = 0, 2, need
+    TwoRanks.struct.buffer[0] = mine.struct.buffer[0]
+    TwoRanks.struct.buffer[1] = silent.struct.buffer[0]
+    seq = tuna_b200.ReduceSequence(gemms, code, TwoRanks)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.tuna_check_device_status(stream) == 0
+    t0 = time.time()
+    seq.run()
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 20.0
+    assert lib.tuna_check_device_status(stream) == -8   # TUNA_ERR_DEVICE_TIMEOUT, and the word is cleared
+    assert lib.tuna_check_device_status(stream) == 0
+    assert bool(torch.isnan(gemms[0][3]).all())           # nothing was summed
+    # the device and the library are still usable: the same GEMM through the plain sequence
+    tuna_b200.MatmulSequence(gemms, code).run()
+    torch.cuda.synchronize()
+    check_parity(gemms[0][3].cpu().numpy(), refs[0], 1e-2)
+    mine.close()
+    silent.close()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")

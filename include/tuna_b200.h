@@ -56,7 +56,7 @@ typedef enum tuna_path {
  * param_map.json, or filled by hand (tuner, tests).  Zero means "default". */
 typedef struct tuna_config {
     int32_t path;          /* tuna_path                                               */
-    int32_t tile_tok;      /* tokens per pass: stream 8|16|32; tstream 16|32|64;      *
+    int32_t tile_tok;      /* tokens per pass: stream 8|16|32; tstream 16|32|64|128;  *
                             * umma 16|32|64|128|256                                   */
     int32_t rows_per_warp; /* stream: 32-row blocks per warp (1|2)                    */
     int32_t warps_m;       /* stream: consumer warps along output rows (power of 2)   */

@@ -85,6 +85,12 @@ def test_tstream_token_tiles_and_passes(n, tile_tok, row_blocks, k_steps):
     _run(640, n, 520, seed=n, tile_tok=tile_tok, row_blocks=row_blocks, k_steps=k_steps)
 
 
+@pytest.mark.parametrize("m,n,k", [(640, 128, 512), (640, 100, 520), (1024, 300, 2048), (264, 129, 200), (28672, 256, 4096)])
+def test_tstream_128_token_tiles(m, n, k):
+    """Passes of 128 tokens (128-column slots, one row block): every stage layout, ragged token counts."""
+    _run(m, n, k, seed=m + n, tile_tok=128, row_blocks=1, k_steps=4)
+
+
 @pytest.mark.parametrize("k_steps", [4, 8])
 @pytest.mark.parametrize("m,n,k,tile_tok", [
     (640, 64, 512, 64), (640, 33, 1024, 64), (1024, 32, 2048, 32),   # 5-D view (m % 32 = 0, k % 64 = 0), larger token tiles

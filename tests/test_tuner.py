@@ -44,8 +44,9 @@ def test_config_fields_round_trip():
 def test_path_is_part_of_the_search():
     assert tuner.candidate_paths(16) == ("tstream", "stream")
     assert "umma" in tuner.candidate_paths(64) and "tstream" in tuner.candidate_paths(64)
-    assert tuner.candidate_paths(2048) == ("umma",)
+    assert tuner.candidate_paths(2048) == ("tstream", "umma")
     assert tuner.tile_tok_for("tstream", 9) == 16 and tuner.tile_tok_for("tstream", 40) == 64
+    assert tuner.tile_tok_for("tstream", 65) == 128 and tuner.tile_tok_for("tstream", 2048) == 128
     assert tuner.tile_tok_for("stream", 8) == 8 and tuner.tile_tok_for("umma", 2048) == 256
 
 
@@ -56,3 +57,7 @@ def test_tstream_validity(tuna_lib):
     assert not tuner.is_valid(tuna_lib, 4096, 64, 4096, too_wide)
     bad_steps = tuner.to_config("tstream", 16, dict(row_blocks=1, k_steps=16))
     assert not tuner.is_valid(tuna_lib, 4096, 16, 4096, bad_steps)
+    # 128-token tiles: one row block and 128-column slots only
+    assert tuner.is_valid(tuna_lib, 4096, 300, 4096, tuner.to_config("tstream", 128, dict(row_blocks=1, k_steps=4)))
+    assert not tuner.is_valid(tuna_lib, 4096, 300, 4096, tuner.to_config("tstream", 128, dict(row_blocks=2, k_steps=4)))
+    assert not tuner.is_valid(tuna_lib, 4096, 300, 4096, tuner.to_config("tstream", 128, dict(row_blocks=1, k_steps=8)))

@@ -252,10 +252,10 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_w4a16_tstream_kernel(const
     constexpr uint32_t kXTileBytes = N_TILE * 128;
     constexpr uint32_t kXStageBytes = kXTiles * kXTileBytes;
     // activation stages (TMA -> MMA); up to 32 tokens the ring has to fit below the lookup table (shared address 0x10000)
-    constexpr int kXS = (N_TILE == 64 || 4 * kXStageBytes + 4096 > 0x10000) ? 3 : 4;
+    constexpr int kXS = (N_TILE >= 64 || 4 * kXStageBytes + 4096 > 0x10000) ? 3 : 4;
     constexpr uint32_t kStepBytes = 16 * 128;                         // one step of a weight stage: 16 row groups x 128 bytes
     static_assert(kXS <= kTsMaxXStages, "barrier arrays too small");
-    static_assert(N_TILE == 64 || kXS * kXStageBytes + 4096 <= 0x10000, "the activation ring must end below the lookup table");
+    static_assert(N_TILE > 32 || kXS * kXStageBytes + 4096 <= 0x10000, "the activation ring must end below the lookup table");
     static_assert(kXStageBytes % 1024 == 0 && kSlotBytes % 1024 == 0, "swizzle atoms are 1024 bytes");
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[2 * kTsMaxASlots + 2 * kTsMaxXStages + 4 + 2 * kTsMaxWStages];
@@ -734,11 +734,19 @@ static int ts_steps(const tuna_config &c) { return c.k_steps == 4 ? 4 : 8; }
 
 int gemm_tstream_normalize_config(int m, int n, int k, int sm_count, tuna_config *c)
 {
-    if (c->tile_tok == 0) c->tile_tok = (n <= 16) ? 16 : (n <= 32 ? 32 : 64);
-    if (c->tile_tok != 16 && c->tile_tok != 32 && c->tile_tok != 64) return TUNA_ERR_BAD_CONFIG;
+    if (c->tile_tok == 0) c->tile_tok = (n <= 16) ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : 128));
+    if (c->tile_tok != 16 && c->tile_tok != 32 && c->tile_tok != 64 && c->tile_tok != 128) return TUNA_ERR_BAD_CONFIG;
+    if (c->tile_tok == 128) {
+        // 128-token tiles (token counts above 64 run as passes of 128): the tensor pipe needs 64 clocks
+        // per MMA there, as long as the dequantisation of 16 columns, so a slot is 128 columns (8 MMAs per
+        // wait and commit are enough) and a tile one row block (the accumulators take 2 x 128 columns)
+        if (c->row_blocks == 0) c->row_blocks = 1;
+        if (c->k_steps == 0) c->k_steps = 4;
+        if (c->row_blocks != 1 || c->k_steps != 4) return TUNA_ERR_BAD_CONFIG;
+    }
     // two row blocks share an activation stage when the matrix is tall enough for 32-KB units to balance
     if (c->row_blocks == 0) c->row_blocks = (m >= 8192 && c->tile_tok <= 32) ? 2 : 1;
-    if ((c->row_blocks != 1 && c->row_blocks != 2 && c->row_blocks != 4) || c->row_blocks * c->tile_tok > 64)
+    if ((c->row_blocks != 1 && c->row_blocks != 2 && c->row_blocks != 4) || (c->tile_tok <= 64 && c->row_blocks * c->tile_tok > 64))
         return TUNA_ERR_BAD_CONFIG;
     if (c->ctas < 0) return TUNA_ERR_BAD_CONFIG;
     if (c->ctas == 0 || c->ctas > sm_count) c->ctas = sm_count;
@@ -804,6 +812,8 @@ static int launch_ts_dispatch(const TsLaunch<MAXG> &L, int tile_tok, int steps, 
         case 6441: return launch_ts<64, 4, MAXG, 1>(L, ctas, stream);
         case 6480: return launch_ts<64, 8, MAXG, 0>(L, ctas, stream);
         case 6481: return launch_ts<64, 8, MAXG, 1>(L, ctas, stream);
+        case 12840: return launch_ts<128, 4, MAXG, 0>(L, ctas, stream);
+        case 12841: return launch_ts<128, 4, MAXG, 1>(L, ctas, stream);
         default: return TUNA_ERR_BAD_CONFIG;
     }
 }

@@ -64,16 +64,14 @@ def candidate_paths(n: int) -> tuple:
     (the reference's table has one kernel and tunes its tile per bucket, kernel.cu:3022-3155)."""
     if n <= 32:
         return ("tstream", "stream")
-    if n <= 128:
-        return ("tstream", "umma")
-    return ("umma",)
+    return ("tstream", "umma")  # above 64 tokens the streaming kernel runs passes of 128 tokens
 
 
 def tile_tok_for(path: str, n: int) -> int:
     if path == "stream":
         return 8 if n <= 8 else 16 if n <= 16 else 32
     if path == "tstream":
-        return 16 if n <= 16 else 32 if n <= 32 else 64
+        return 16 if n <= 16 else 32 if n <= 32 else 64 if n <= 64 else 128
     return min(make_configs.token_bucket(n), 256)
 
 

@@ -473,6 +473,36 @@ def run_extras(dev, stream, timed, code, steps):
         del sets, g, gs, seq, o_all
         torch.cuda.empty_cache()
 
+    # ---- Mixtral's experts as separate GEMMs with per-expert token lists (the reference benchmarks one combined
+    # GEMM over all experts instead, make_configs.py:105-106): 16 tokens routed to 2 of 8 experts each
+    layers, counts = 4, [7, 5, 4, 4, 3, 3, 3, 3]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(99)
+    gemms, total = [], 0
+    for _ in range(layers):
+        for m, k in ((28672, 4096), (4096, 14336)):  # gate+up, down of every expert
+            for n_e in counts:
+                q = torch.randint(0, 256, (m * k // 2,), dtype=torch.uint8, device=dev, generator=gen)
+                sc = (0.005 + 0.015 * torch.rand(m, device=dev, generator=gen)).half().float()
+                x = torch.randn((n_e, k), device=dev, generator=gen).half()
+                o = torch.empty((n_e, m), dtype=torch.float16, device=dev)
+                gemms.append((x, q, sc, o, m, n_e, k))
+                total += alg_bytes(m, n_e, k)
+    seq = tuna_b200.MatmulSequence(gemms, code)
+    with torch.cuda.stream(stream):
+        seq.run()
+        stream.synchronize()
+        gs = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gs, stream=stream):
+            seq.run()
+    ms_seq = timed(gs.replay, max(3, steps // 4), 2, 20)
+    hbm, _ = measured_peak()
+    out["mixtral8x7b_experts_m16"] = {"layers": layers, "experts": 8, "tokens_per_expert": counts, "gemms": len(gemms), "bytes_per_sweep": total,
+                                      "sequence": {"ms_per_sweep": ms_seq, "gbs": total / (ms_seq * 1e-3) / 1e9, "frac_hbm": total / (ms_seq * 1e-3) / 1e9 / hbm,
+                                                   "api": "tuna_matmul_sequence with one entry per expert (its own token count), CUDA graph replay"}}
+    del gemms, seq, gs
+    torch.cuda.empty_cache()
+
     # ---- token sweep on the Llama-70B gate+up shape (BASELINE config 4)
     m, k = 57344, 8192
     gen = torch.Generator(device=dev)

@@ -69,6 +69,17 @@ def main():
     for g, ref in zip(gemms, refs):
         got = g[3].cpu().numpy()
         assert np.abs(got.astype(np.float32) - ref).max() / np.abs(ref).max() <= 1e-2
+    # the tensor-parallel layer class with the fused sum instead of its all-reduce
+    m, n, k = 1024, 16, 4096
+    x, q, absmax, codebook = orc.synth_inputs(m, n, k, 900)
+    layer = sharding.RowParallelLinear(torch.from_numpy(q).to(dev), torch.from_numpy(absmax).to(dev), code, m, k, exchange=ex)
+    xs = layer.slice_input(torch.from_numpy(x).to(dev))
+    out = torch.full((n, m), float("nan"), dtype=torch.float16, device=dev)
+    for _ in range(2):
+        layer.forward(xs, out)
+    torch.cuda.synchronize()
+    ref = orc.matmul_ref(x, q, absmax, codebook, m, n, k)
+    assert np.abs(out.cpu().numpy().astype(np.float32) - ref).max() / np.abs(ref).max() <= 1e-2
     dist.barrier()
     ex.close()
     dist.barrier()

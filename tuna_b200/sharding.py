@@ -89,11 +89,16 @@ class RowParallelLinear:
 
     Partials travel as fp16, like the fp16 split-K partials of the reference
     (kernel.cu:2719, 2742); `reduce_dtype=torch.float32` keeps them in fp32.
+    With `exchange` (a `tuna_b200.Exchange` over the same group, at least
+    `ReduceSequence.exchange_bytes([(m, 64, k_shard)], world)` bytes) and up to 64 tokens the
+    sum is fused into the launch instead (`tuna_matmul_sequence_reduce`): no collective.
     """
 
     def __init__(self, q, absmax, code, m: int, k: int, group=None,
-                 matmul_fn: Optional[Callable] = None, reduce_dtype=torch.float16):
+                 matmul_fn: Optional[Callable] = None, reduce_dtype=torch.float16, exchange=None):
         self.group = group
+        self.exchange = exchange
+        self._fused = {}  # (x pointer, out pointer, n) -> ReduceSequence
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.m, self.k = m, k
@@ -111,6 +116,16 @@ class RowParallelLinear:
         n = x_shard.shape[0]
         if out is None:
             out = torch.empty((n, self.m), dtype=torch.float16, device=x_shard.device)
+        if self.exchange is not None and n <= 64:
+            from .ops import ReduceSequence
+
+            key = (x_shard.data_ptr(), out.data_ptr(), n)
+            seq = self._fused.get(key)
+            if seq is None:  # a sequence holds addresses: one per (input, output) pair that was seen
+                seq = ReduceSequence([(x_shard, self.q.reshape(-1), self.absmax, out, self.m, n, self.k_shard)], self.code, self.exchange)
+                self._fused = {key: seq}
+            seq.run()
+            return out
         self.matmul_fn(x_shard, self.q, self.absmax, self.code, out, self.m, n, self.k_shard)
         if self.world > 1:
             if self.reduce_dtype == torch.float16:

@@ -51,3 +51,24 @@ def test_algorithmic_bytes():
     # m*k/2 packed weights + 4m scales + 64 codebook + 2nk activations + 2nm outputs
     assert bench.alg_bytes(28672, 16, 4096) == 59883584
     assert bench.alg_bytes(4096, 16, 14336) == 29966400
+
+
+def test_neighbouring_copies_are_merged():
+    """HostSequence issues runs of tensors that are adjacent on both sides as one copy of the same bytes."""
+    import torch
+
+    from tuna_b200.ops import _merge_copies
+
+    dst, src = torch.zeros(100, dtype=torch.float16), torch.arange(100, dtype=torch.float16)
+    copies = [(dst[0:10], src[0:10]), (dst[10:30], src[10:30]),   # adjacent on both sides: one run
+              (dst[40:50], src[40:50]),                            # a gap on both sides: its own copy
+              (dst[50:60], src[60:70])]                            # adjacent destinations, sources are not
+    merged = _merge_copies(copies)
+    assert [d.numel() * d.element_size() for d, _ in merged] == [60, 20, 20]
+    for d, s in merged:
+        d.copy_(s)
+    want = torch.zeros(100, dtype=torch.float16)
+    want[0:30], want[40:50], want[50:60] = src[0:30], src[40:50], src[60:70]
+    assert torch.equal(dst, want)
+    other = torch.zeros(10, dtype=torch.float16)
+    assert len(_merge_copies([(dst[0:10], src[0:10]), (other, src[10:20])])) == 2  # different allocations never merge

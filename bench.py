@@ -999,7 +999,7 @@ def main():
 # algorithmic), scaled by the layers - traffic grows in proportion, every layer has its own weights.
 DRAM_TRAFFIC_PER_LAUNCH: dict = {
     ("sequence", "mistral7b_mlp_m16", 1): (8 * (356.87e6 + 8.14e6), "ncu capture of `python bench.py --layers 4 --steps 1 --warmup 3 "
-                                            "--no-cpu-baseline --no-extras --inner 1` (one sequence launch), scaled x8 to the 32 layers"),
+                                            "--no-cpu-baseline --no-extras --inner 1` (one sequence launch; kernel as of commit 8564eba), scaled x8 to the 32 layers"),
 }
 
 if __name__ == "__main__":

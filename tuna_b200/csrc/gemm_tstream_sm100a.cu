@@ -780,6 +780,15 @@ static int launch_ts(const TsLaunch<MAXG> &L, int ctas, cudaStream_t stream)
             if (cudaFuncSetAttribute(gemm_w4a16_tstream_kernel<N_TILE, STEPS, MAXG, WMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kTsSmemDynamic) != cudaSuccess)
                 return TUNA_ERR_NO_DEVICE;
+            // The kernel places its lookup table at shared address 0x10000 and what lies below it right
+            // after the start of dynamic shared memory, which must therefore begin within the first 4 KB
+            // (static shared memory of the kernel + what the system reserves per block; the kernel checks too).
+            cudaFuncAttributes fa;
+            int reserved = 0;
+            if (cudaFuncGetAttributes(&fa, gemm_w4a16_tstream_kernel<N_TILE, STEPS, MAXG, WMODE>) != cudaSuccess ||
+                cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev) != cudaSuccess)
+                return TUNA_ERR_NO_DEVICE;
+            if ((fa.sharedSizeBytes + (size_t)reserved + 1023) / 1024 * 1024 > 4096) return TUNA_ERR_NO_DEVICE;
             attr_set[dev] = true;
         }
     }
